@@ -2,7 +2,7 @@
 
 Every plane (a layer's cache) says through its `CacheSpec` what it stores a token: keys and values, or one
 tensor; how wide; for all positions or a window; in pages of how many tokens; in which dtype.  Planes with the
-same window and page size form a cache group: one page pool and one block table per request, managed on the
+same window (or chunk) and page size form a cache group: one page pool and one block table per request, managed on the
 host by `KvCacheManager` (C++).  The reference keeps one buffer [2, layers, num_blocks, block_size, kv_heads,
 head_dim] (vllm-oxide, crates/vllm-oxide/src/attention/mod.rs:42-85); here every plane has a [tensors, num_pages,
 kv_heads, block_size, head_dim] buffer: planes of different widths can share a group, and the keys of one head
@@ -29,6 +29,7 @@ class CacheGroup:
     block_size: int
     num_blocks: int
     planes: List[int]
+    chunk: int = 0
 
 
 class PagedCache:
@@ -37,17 +38,19 @@ class PagedCache:
                  gpu_memory_utilization: float = 0.9, prefix_caching: bool = False, reserve_bytes: int = 0):
         self.dtype, self.device, self.block_size = dtype, device, block_size
         for s in cache_specs:
-            if s is not None and (s.tensors not in (1, 2) or s.kv_heads <= 0 or s.head_dim <= 0 or s.window < 0
-                                  or (s.block_size is not None and s.block_size <= 0)):
+            if s is not None and (s.tensors not in (1, 2) or s.kv_heads <= 0 or s.head_dim <= 0 or s.window < 0 or s.chunk < 0
+                                  or (s.block_size is not None and s.block_size <= 0)
+                                  or ((s.value_heads or s.value_dim) and s.tensors != 2) or min(s.value_shape()) <= 0):
                 raise ValueError(f"unusable cache spec {s}")
         page_size = lambda s: s.block_size or block_size
-        keys = sorted({(s.window, page_size(s)) for s in cache_specs if s is not None})
+        key_of = lambda s: (s.window, s.chunk, page_size(s))
+        keys = sorted({key_of(s) for s in cache_specs if s is not None})
         if not keys:
-            keys = [(0, block_size)]   # a model without paged keys still gets block tables (of a pool nobody reads)
-        self.groups: List[CacheGroup] = [CacheGroup(w, bs, 0, []) for w, bs in keys]
+            keys = [(0, 0, block_size)]   # a model without paged keys still gets block tables (of a pool nobody reads)
+        self.groups: List[CacheGroup] = [CacheGroup(w, bs, 0, [], c) for w, c, bs in keys]
         for plane, s in enumerate(cache_specs):
             if s is not None:
-                self.groups[keys.index((s.window, page_size(s)))].planes.append(plane)
+                self.groups[keys.index(key_of(s))].planes.append(plane)
         width = lambda s: torch.empty((), dtype=s.dtype or dtype).element_size() * s.elements_per_token()
         token_bytes = sum(width(s) for s in cache_specs if s is not None)
         if num_blocks is None:
@@ -67,8 +70,14 @@ class PagedCache:
             if s is None:
                 self.planes.append(None)
                 continue
-            gi = keys.index((s.window, page_size(s)))
+            gi = keys.index(key_of(s))
             g = self.groups[gi]
+            if s.tensors == 2 and s.value_shape() != (s.kv_heads, s.head_dim):
+                vh, vd = s.value_shape()
+                k = torch.zeros((g.num_blocks, s.kv_heads, g.block_size, s.head_dim), dtype=s.dtype or dtype, device=device)
+                v = torch.zeros((g.num_blocks, vh, g.block_size, vd), dtype=s.dtype or dtype, device=device)
+                self.planes.append(CachePlane(k, v, gi, g.block_size, None))
+                continue
             buf = torch.zeros((s.tensors, g.num_blocks, s.kv_heads, g.block_size, s.head_dim), dtype=s.dtype or dtype,
                               device=device)
             self.planes.append(CachePlane(buf[0], buf[1] if s.tensors == 2 else None, gi, g.block_size, buf))
@@ -77,12 +86,12 @@ class PagedCache:
             None if s is None else torch.zeros((num_state_slots, *s.shape), dtype=s.dtype, device=device)
             for s in state_specs]
         self.manager = host.KvCacheManager(
-            [host.GroupSpec(g.block_size, g.num_blocks, g.window) for g in self.groups], num_state_slots,
+            [host.GroupSpec(g.block_size, g.num_blocks, g.window, g.chunk) for g in self.groups], num_state_slots,
             # state of fixed size is not snapshotted at page boundaries: with such a layer nothing is skipped on a hit
             prefix_caching and not any(s is not None for s in state_specs))
 
     def bytes(self) -> int:
-        total = sum(p.data.numel() * p.data.element_size() for p in self.planes if p is not None)
+        total = sum(t.numel() * t.element_size() for p in self.planes if p is not None for t in (p.k, p.v) if t is not None)
         return total + sum(s.numel() * s.element_size() for s in self.states if s is not None)
 
     @property

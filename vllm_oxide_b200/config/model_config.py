@@ -381,3 +381,126 @@ class KesozenConfig:
         if self.loop is not None:
             d["loop"] = {"start": self.loop[0], "stop": self.loop[1], "times": self.loop[2]}
         return d
+
+
+# ---------------------------------------------------------------------------------------------------------------
+_RAKIZEN_MIXERS = ("attention", "attention_2")
+
+
+def _check_moe(mlp: dict, w: str) -> None:
+    """`mlp` = null | {kind: dense, ff} | {kind: moe, expert{ff}, router{experts, top, groups{count, keep}}} as the
+    layer-list configurations write it."""
+    if not isinstance(mlp, dict) or mlp.get("kind") not in ("dense", "moe"):
+        raise ConfigError(f"{w}: mlp must be null or of kind 'dense' or 'moe', got {mlp!r}")
+    if mlp["kind"] == "dense":
+        _need(mlp, "ff", int, w + ".mlp")
+        return
+    _need(_sub(mlp, "expert", w + ".mlp"), "ff", int, w + ".mlp.expert")
+    r = _sub(mlp, "router", w + ".mlp")
+    E, top = _need(r, "experts", int, w + ".mlp.router"), _need(r, "top", int, w + ".mlp.router")
+    count = keep = 1
+    if r.get("groups") is not None:
+        g = _sub(r, "groups", w + ".mlp.router")
+        count, keep = _need(g, "count", int, w + ".mlp.router.groups"), _need(g, "keep", int, w + ".mlp.router.groups")
+    if min(E, top, count, keep) <= 0 or E % count or keep > count or top > (E // count) * keep:
+        raise ConfigError(f"{w}: {E} experts in {count} groups of which {keep} are kept cannot give {top} choices")
+    if r.get("scale") is not None:
+        _need(r, "scale", float, w + ".mlp.router")
+
+
+@dataclass(frozen=True)
+class RakizenLayer:
+    type: str                   # "attention" | "attention_2"
+    mixer: dict                 # the mixer's sizes and constants, as config.json gives them
+    mlp: Optional[dict]         # None, {"kind": "dense", "ff"} or {"kind": "moe", "expert": {"ff"}, "router": {...}}
+
+
+@dataclass(frozen=True)
+class RakizenConfig:
+    """Rakizen: a decoder whose layers are listed one by one in config.json.  A layer has ONE layer norm (gain and bias)
+    that its mixer and its feed-forward both read; their outputs are added to one float residual stream together.  The
+    mixer is `attention` (every head the difference of two softmax maps over shared values, scores capped by a tanh, keys
+    visible inside blocks of `mask.size` positions, a unit norm per head, an output gate; nothing is rotated) or
+    `attention_2` (q and k normed over their whole projections, the first `rot.dims` elements of each head rotated in
+    neighbouring pairs, capped scores, a sliding window of `mask.size` positions).  The feed-forward is a gated SiLU layer,
+    a mixture of such layers routed by sigmoid scores among groups, or absent.  A stretch of the layers (`loop`: start,
+    stop, times) may run several times in a row with the same weights, every pass with a cache of its own.  Keys: `vocab`,
+    `width`, `norm.eps`, `layers[i]` = {type, mixer{...}, mlp}, `loop`.  There is no largest position."""
+    vocab: int
+    width: int
+    eps: float
+    layers: tuple
+    loop: Optional[tuple] = None      # (start, stop, times)
+    torch_dtype: str = "bfloat16"
+
+    architecture = "Rakizen"
+
+    @classmethod
+    def from_dict(cls, d: dict, where: str = "config.json") -> "RakizenConfig":
+        layers = d.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError(f"{where}: 'layers' must be a non-empty list")
+        out = []
+        for i, layer in enumerate(layers):
+            w = f"{where}: layers[{i}]"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"{w} must be an object")
+            kind = layer.get("type")
+            if kind not in _RAKIZEN_MIXERS:
+                raise ConfigError(f"{w}: type {kind!r} is not one of {list(_RAKIZEN_MIXERS)}")
+            m = _sub(layer, "mixer", w)
+            for k in ("heads", "kv_heads", "dim", "vdim"):
+                if _need(m, k, int, w) <= 0:
+                    raise ConfigError(f"{w}: {k} must be positive")
+            if m["heads"] % m["kv_heads"]:
+                raise ConfigError(f"{w}: heads {m['heads']} is not a multiple of kv_heads {m['kv_heads']}")
+            _need(m, "scale", float, w)
+            if m.get("softcap") is not None and _need(m, "softcap", float, w) < 0:
+                raise ConfigError(f"{w}: softcap must not be negative")
+            if m.get("mask") is not None and _need(_sub(m, "mask", w), "size", int, w + ".mask") <= 0:
+                raise ConfigError(f"{w}: mask.size must be positive")
+            if kind == "attention":
+                _need(m, "diff", float, w)
+            elif m.get("rot") is not None:
+                rot = _sub(m, "rot", w)
+                _need(rot, "base", float, w + ".rot")
+                dims = rot.get("dims")
+                if isinstance(dims, bool) or not isinstance(dims, int) or dims < 0 or dims % 2 or dims > m["dim"]:
+                    raise ConfigError(f"{w}: rot.dims {dims!r} must be even and between 0 and dim {m['dim']}")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                _check_moe(mlp, w)
+            out.append(RakizenLayer(kind, dict(m), None if mlp is None else dict(mlp)))
+        loop = d.get("loop")
+        if loop is not None:
+            loop = _sub(d, "loop", where)
+            start, stop = loop.get("start"), loop.get("stop")
+            times = _need(loop, "times", int, where + ".loop")
+            for v in (start, stop):
+                if isinstance(v, bool) or not isinstance(v, int):
+                    raise ConfigError(f"{where}: loop.start and loop.stop must be integers")
+            if not 0 <= start <= stop <= len(out) or times < 1:
+                raise ConfigError(f"{where}: loop {start}..{stop} x {times} does not lie within the {len(out)} layers")
+            loop = (start, stop, times)
+        dtype = d.get("torch_dtype", d.get("dtype", "bfloat16"))
+        if not isinstance(dtype, str) or dtype not in _DTYPE_NAMES:
+            raise ConfigError(f"{where}: torch_dtype {dtype!r} is not one of {sorted(set(_DTYPE_NAMES))}")
+        return cls(vocab=_need(d, "vocab", int, where), width=_need(d, "width", int, where),
+                   eps=_need(_sub(d, "norm", where), "eps", float, where + ".norm"), layers=tuple(out), loop=loop,
+                   torch_dtype=_DTYPE_NAMES[dtype])
+
+    def runs(self):
+        """The layers in the order they run."""
+        n = len(self.layers)
+        if self.loop is None:
+            return list(range(n))
+        start, stop, times = self.loop
+        return list(range(start)) + list(range(start, stop)) * times + list(range(stop, n))
+
+    def to_dict(self) -> dict:
+        d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.eps},
+             "layers": [{"type": l.type, "mixer": dict(l.mixer), "mlp": None if l.mlp is None else dict(l.mlp)}
+                        for l in self.layers]}
+        if self.loop is not None:
+            d["loop"] = {"start": self.loop[0], "stop": self.loop[1], "times": self.loop[2]}
+        return d

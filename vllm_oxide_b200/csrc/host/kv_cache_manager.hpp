@@ -27,6 +27,15 @@ struct GroupSpec {
   int block_size = 16;
   int num_blocks = 1;
   int window = 0;  // 0: every key is kept; W > 0: only positions > query - W are read
+  int chunk = 0;   // C > 0: a query reads only positions of its own block of C positions (blocks counted from 0)
+  bool limited() const { return window > 0 || chunk > 0; }
+  // The lowest position that a query at a position >= next can still read.
+  int first_needed(int next) const {
+    int lo = 0;
+    if (window > 0) lo = std::max(lo, next - window + 1);
+    if (chunk > 0) lo = std::max(lo, next / chunk * chunk);
+    return lo;
+  }
 };
 
 class KvCacheManager {
@@ -37,7 +46,7 @@ class KvCacheManager {
     if (num_state_slots <= 0) throw PoolError("KvCacheManager: at least one state slot is needed");
     bool same = true;
     for (const auto& g : groups) {
-      if (g.window < 0) throw PoolError("KvCacheManager: negative window");
+      if (g.window < 0 || g.chunk < 0) throw PoolError("KvCacheManager: negative window or chunk");
       pools_.emplace_back(g.num_blocks, g.block_size);
       same = same && g.block_size == groups[0].block_size;
     }
@@ -89,7 +98,7 @@ class KvCacheManager {
         pools_[g].retain(found[g][i]);
         r.tables[g][i] = found[g][i];
       }
-      if (specs_[g].window > 0) r.released_upto[g] = lo;
+      if (specs_[g].limited()) r.released_upto[g] = lo;
     }
     r.page_hashes.assign(hashes.begin(), hashes.begin() + hits);
     return hits * specs_[0].block_size;
@@ -147,10 +156,9 @@ class KvCacheManager {
   void advance(int64_t id, int num_computed) {
     Req& r = req(id);
     for (size_t g = 0; g < specs_.size(); ++g) {
-      const int w = specs_[g].window;
-      if (w <= 0) continue;
+      if (!specs_[g].limited()) continue;
       const int bs = specs_[g].block_size;
-      const int first_needed = num_computed - w + 1;  // lowest position still readable
+      const int first_needed = specs_[g].first_needed(num_computed);  // lowest position still readable
       auto& t = r.tables[g];
       for (int p = r.released_upto[g]; p < static_cast<int>(t.size()) && (p + 1) * bs <= first_needed; ++p) {
         if (t[p] >= 0) { pools_[g].release(t[p]); t[p] = -1; }
@@ -255,9 +263,8 @@ class KvCacheManager {
   // The first page of group g that a query at a position >= pages * block_size can read (0 for a group that keeps
   // all keys): the same rule by which advance() gives pages back.
   int first_page_needed(size_t g, int pages) const {
-    const int w = specs_[g].window;
-    if (w <= 0) return 0;
-    const int first_needed = pages * specs_[g].block_size - w + 1;
+    if (!specs_[g].limited()) return 0;
+    const int first_needed = specs_[g].first_needed(pages * specs_[g].block_size);
     return first_needed <= 0 ? 0 : std::min(pages, first_needed / specs_[g].block_size);
   }
 
@@ -277,7 +284,7 @@ class KvCacheManager {
       for (size_t g = 0; g < specs_.size(); ++g) {
         const int page = pools_[g].lookup(h, tokens + i * bs, bs);
         ids[g].push_back(page);
-        all = all && (page >= 0 || specs_[g].window > 0);
+        all = all && (page >= 0 || specs_[g].limited());
       }
       if (!all) break;
       hs.push_back(h);

@@ -13,6 +13,11 @@
 // the keys.  Scale 1/sqrt(hd) is applied to the score as the reference does
 // (vllm-oxide, crates/vllm-oxide/src/models/qwen3.rs:204-209); query head h reads key/value
 // head h / (nh/kvh).
+//
+// Options that other mixers use: the value plane may have its own head size and fewer heads than the key plane (value
+// head = key head * vkvh / kvh: neighbouring key heads share a value head); `softcap` > 0 bends the scaled score to
+// softcap * tanh(score / softcap); `chunk` > 0 moves lo to the start of the query's block of `chunk` positions (blocks
+// counted from position 0), so a query sees only keys of its own block; the output may be stored as float whatever T.
 #include "common.cuh"
 
 namespace vob {
@@ -68,10 +73,10 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
                                const int* __restrict__ token_req, const int* __restrict__ positions,
                                const int* __restrict__ skip_single_cu_q, int nh, int kvh, int hd, int vd, int block_size,
                                int window, float scale, long num_pages, int sink, const T* gate, long gate_stride,
-                               int* err) {
+                               int vkvh, int v_row, float softcap, int chunk, int out_float, int* err) {
   extern __shared__ float smem[];
   float* qs = smem;                        // [hd]
-  float* accs = smem + hd;                 // [ATT_WARPS][hd]
+  float* accs = smem + hd;                 // [ATT_WARPS][vd]
   __shared__ float ms[ATT_WARPS], ls[ATT_WARPS];
   pdl_launch_dependents();
   pdl_wait();
@@ -82,7 +87,9 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
   const int pos = positions[t];
   const int kh = h / (nh / kvh);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int vh = (int)((long)kh * vkvh / kvh);
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, pos / chunk * chunk);
   const T* qrow = q + (size_t)t * q_stride + (size_t)h * hd;
   for (int i = threadIdx.x; i < hd; i += blockDim.x) qs[i] = to_f<T>(qrow[i]);
   __syncthreads();
@@ -97,13 +104,17 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
     const int key = tile * 32 + lane;
     const bool valid = key >= lo && key <= pos;
     long row = -1;  // element offset of this key's row for kv head kh
+    int page = -1;
     if (valid) {
-      const int page = table[key / block_size];
-      if (page < 0 || page >= num_pages) atomicOr(err, VOB_ERR_PAGE);
+      page = table[key / block_size];
+      if (page < 0 || page >= num_pages) { atomicOr(err, VOB_ERR_PAGE); page = -1; }
       else row = (((long)page * kvh + kh) * block_size + key % block_size) * (long)hd;
     }
     float s = -INFINITY;
-    if (row >= 0) s = dot_row<T>(qs, kcache + row, hd) * scale;
+    if (row >= 0) {
+      s = dot_row<T>(qs, kcache + row, hd) * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+    }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = (row >= 0) ? expf(s - m_new) : 0.f;
     const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
@@ -111,10 +122,10 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
 #pragma unroll
     for (int j = 0; j < ATT_MAXD; ++j) acc[j] *= corr;
     for (int kk = 0; kk < 32; ++kk) {
-      const long rk = __shfl_sync(0xffffffffu, row, kk);
-      if (rk < 0) continue;
+      const int pg = __shfl_sync(0xffffffffu, page, kk);
+      if (pg < 0) continue;
       const float pk = __shfl_sync(0xffffffffu, p, kk);
-      const T* vrow = vcache + rk;
+      const T* vrow = vcache + (((long)pg * vkvh + vh) * block_size + (tile * 32 + kk) % block_size) * (long)v_row;
 #pragma unroll
       for (int j = 0; j < ATT_MAXD; ++j) {
         const int d = lane + 32 * j;
@@ -127,7 +138,7 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
 #pragma unroll
   for (int j = 0; j < ATT_MAXD; ++j) {
     const int d = lane + 32 * j;
-    if (d < vd) accs[warp * hd + d] = acc[j];
+    if (d < vd) accs[warp * vd + d] = acc[j];
   }
   __syncthreads();
   float mm = -INFINITY;
@@ -143,12 +154,14 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
   }
   // a gate: the head's output times sigmoid of one number of the token's row
   const float gt = gate ? 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * gate_stride + h]))) : 1.f;
-  T* orow = out + (size_t)t * nh * vd + (size_t)h * vd;
+  const size_t obase = (size_t)t * nh * vd + (size_t)h * vd;
   for (int d = threadIdx.x; d < vd; d += blockDim.x) {
     float o = 0.f;
 #pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) o += accs[w * hd + d] * f[w];
-    orow[d] = from_f<T>(lt > 0.f ? o / lt * gt : 0.f);
+    for (int w = 0; w < ATT_WARPS; ++w) o += accs[w * vd + d] * f[w];
+    o = lt > 0.f ? o / lt * gt : 0.f;
+    if (out_float) reinterpret_cast<float*>(out)[obase + d] = o;
+    else out[obase + d] = from_f<T>(o);
   }
 }
 
@@ -161,26 +174,33 @@ using namespace vob;
 // read (vd = hd: all of it; less when keys and values are one row and the key is the longer one).  `sink`: the softmax
 // has a silent extra entry of score 0 (weights exp(s) / (1 + sum exp(s))); `gate` (rows of gate_stride elements, one
 // number a head): head h of token t is multiplied by sigmoid(gate[t, h]).
+// vkvh, v_row: heads and head size of the value plane [num_pages, vkvh, block_size, v_row] (0: those of the key plane);
+// softcap, chunk: see above (0: off); out_float: out is float whatever `dtype`.
 VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
                                         const int* block_tables, int table_stride, const int* token_req,
                                         const int* positions, const int* skip_single_cu_q, int T, int nh, int kvh, int hd,
                                         int vd, int block_size,
                                         int window, float scale, long num_pages, int sink, const void* gate,
-                                        long gate_stride, int dtype, int* err, cudaStream_t stream) {
+                                        long gate_stride, int vkvh, int v_row, float softcap, int chunk, int out_float,
+                                        int dtype, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd <= 0 || hd > 512 || kvh <= 0 || nh % kvh || block_size <= 0 || vd <= 0 || vd > hd) return VOB_UNSUPPORTED;
+  if (vkvh <= 0) vkvh = kvh;
+  if (v_row <= 0) v_row = hd;
+  if (hd <= 0 || hd > 512 || kvh <= 0 || nh % kvh || block_size <= 0 || vd <= 0 || vd > v_row || vd > 512 || kvh % vkvh ||
+      softcap < 0.f || chunk < 0)
+    return VOB_UNSUPPORTED;
   dim3 grid(T, nh);
-  const size_t smem = (size_t)(1 + ATT_WARPS) * hd * sizeof(float);
+  const size_t smem = (size_t)(hd + ATT_WARPS * vd) * sizeof(float);
   if (dtype == VOB_F32)
     return launch_kernel(paged_attention_generic_kernel<float>, grid, ATT_WARPS * 32, smem, stream, (const float*)q, q_stride,
                          (float*)out, (const float*)kcache, (const float*)vcache, block_tables, table_stride, token_req,
                          positions, skip_single_cu_q, nh, kvh, hd, vd, block_size, window, scale, num_pages, sink,
-                         (const float*)gate, gate_stride, err);
+                         (const float*)gate, gate_stride, vkvh, v_row, softcap, chunk, out_float, err);
   if (dtype == VOB_BF16)
     return launch_kernel(paged_attention_generic_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream,
                          (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
                          (const __nv_bfloat16*)vcache, block_tables, table_stride, token_req, positions, skip_single_cu_q,
                          nh, kvh, hd, vd, block_size, window, scale, num_pages, sink, (const __nv_bfloat16*)gate,
-                         gate_stride, err);
+                         gate_stride, vkvh, v_row, softcap, chunk, out_float, err);
   return VOB_BAD_ARGUMENT;
 }

@@ -3,12 +3,15 @@
 //   moe_route     z = W_r h in float (one chain of additions a logit, whatever the batch), s = softmax(z) over all experts;
 //                 the choice is by s + correction, among the experts of the `keep` groups (of `count` equal groups of
 //                 neighbours) whose best choice score is largest; the `top` best are taken and weighted by their plain s,
-//                 as it is (no renormalisation).  Ties go to the lower index.
+//                 as it is (no renormalisation).  Ties go to the lower index.  Options: scores may be sigmoid(z) instead of
+//                 the softmax; there may be no correction; a group may count by the sum of its two best choice scores
+//                 instead of its best; the chosen scores may be divided by their sum (+ 1e-20); and a factor may scale them.
 //   moe_align     sorts the step's (token, choice) pairs by expert: every expert's rows start on a multiple of the product's
 //                 row tile (padding rows name no token), and each row tile knows its expert.  Everything stays on the
 //                 device: the grid of the products is sized for the worst case and tiles past the end return at once.
 //   moe_gemm      C[row] = f(A[row] W_e^T) for the rows of expert e, W stacked [experts, N, K]; A is either gathered by the
-//                 row's token (the first product) or read in place (the second); f is the identity or the squared relu.
+//                 row's token (the first product) or read in place (the second); f is the identity, the squared relu, or
+//                 (rows of W in pairs: gate row, up row) SiLU(gate) * up, which halves the output's width.
 //                 Float accumulation, one chain of fused multiply-adds over k in ascending order for every output element
 //                 (the float path's product, with a tile's expert in front of it).
 //   moe_combine   out[t] = sum_j weight[t, j] * y[row of (t, j)], j in order, in float.
@@ -38,7 +41,7 @@ constexpr int ROUTE_NT = 256;
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_NT)
 moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __restrict__ correction, int* ids, float* weights,
-                 int W, int E, int top, int count, int keep) {
+                 int W, int E, int top, int count, int keep, int sigmoid_scores, int group_top, int normalise, float weight_scale) {
   extern __shared__ __align__(16) float route_smem[];
   float* hrow = route_smem;          // [W]
   float* score = hrow + W;           // [E] softmax
@@ -72,24 +75,35 @@ moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __
   }
   __syncthreads();
   if (warp != 0) return;
-  float m = -INFINITY;
-  for (int e = lane; e < E; e += 32) m = fmaxf(m, score[e]);
-  m = warp_max(m);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) sum += expf(score[e] - m);
-  sum = warp_sum(sum);
-  for (int e = lane; e < E; e += 32) {
-    const float s = expf(score[e] - m) / sum;
-    score[e] = s;
-    choice[e] = s + correction[e];
+  if (sigmoid_scores) {
+    for (int e = lane; e < E; e += 32) {
+      const float s = 1.f / (1.f + expf(-score[e]));
+      score[e] = s;
+      choice[e] = correction ? s + correction[e] : s;
+    }
+  } else {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, score[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(score[e] - m);
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) {
+      const float s = expf(score[e] - m) / sum;
+      score[e] = s;
+      choice[e] = correction ? s + correction[e] : s;
+    }
   }
   __syncwarp();
   const int per = E / count;
   if (keep < count) {
     for (int g = lane; g < count; g += 32) {
-      float b = -INFINITY;
-      for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, choice[e]);
-      gbest[g] = b;
+      float b = -INFINITY, b2 = -INFINITY;     // the group's best and second best choice score
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float c = choice[e];
+        if (c > b) { b2 = b; b = c; } else if (c > b2) { b2 = c; }
+      }
+      gbest[g] = (group_top >= 2 && per >= 2) ? b + b2 : b;
     }
     __syncwarp();
     // the `keep` best groups are marked by +inf; then every expert of an unmarked group is shut out
@@ -118,6 +132,12 @@ moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __
       choice[e] = -INFINITY;
     }
     __syncwarp();
+  }
+  if (lane == 0 && (normalise || weight_scale != 1.f)) {
+    float* wt = weights + (size_t)t * top;
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) sum += wt[j];
+    for (int j = 0; j < top; ++j) wt[j] = (normalise ? wt[j] / (sum + 1e-20f) : wt[j]) * weight_scale;
   }
 }
 
@@ -164,7 +184,8 @@ moe_align_kernel(const int* ids, int* slot_of, int* row_token, int* tile_expert,
 // ---------------------------------------------------------------- the experts' products
 constexpr int MG_N = 64, MG_K = 16;
 
-// EPI 0: as it is; 1: squared relu.  GATHER: row r of A is a[row_token[r]], else a[r].
+// EPI 0: as it is; 1: squared relu; 2: SiLU(even column) * odd column into column / 2.  GATHER: row r of A is
+// a[row_token[r]], else a[r].
 template <typename TA, typename TC, int EPI, bool GATHER>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* A, long lda, const TA* __restrict__ W, TC* C, long ldc, const int* row_token,
@@ -219,6 +240,16 @@ moe_gemm_kernel(const TA* A, long lda, const TA* __restrict__ W, TC* C, long ldc
   for (int i = 0; i < 4; ++i) {
     if (src[ty * 4 + i] < 0) continue;
     const int m = m0 + ty * 4 + i;
+    if (EPI == 2) {
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const int n = n0 + tx * 4 + j;
+        if (n + 1 >= N) continue;
+        const float g = acc[i][j];
+        C[(size_t)m * ldc + n / 2] = from_f<TC>(g / (1.f + expf(-g)) * acc[i][j + 1]);
+      }
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
@@ -282,7 +313,7 @@ moe_order_kernel(const int* ids, int* order, int n, int E) {
 
 constexpr int MV_ROWS = 64;       // output features a block
 
-// EPI 0: float as it is; 1: squared relu into bfloat16.  BY_TOKEN: a pair's input row is its token's (pair / top), else its own.
+// EPI 0: float as it is; 1: squared relu into bfloat16; 2: SiLU(even row) * odd row into bfloat16 column row / 2.  BY_TOKEN: a pair's input row is its token's (pair / top), else its own.
 template <int EPI, bool BY_TOKEN>
 __global__ void __launch_bounds__(256)
 moe_gemv_kernel(const __nv_bfloat16* A, long lda, const __nv_bfloat16* __restrict__ W, void* C, long ldc, const int* ids,
@@ -324,6 +355,18 @@ moe_gemv_kernel(const __nv_bfloat16* A, long lda, const __nv_bfloat16* __restric
           acc[r] = fmaf(wf.y, xf.y, acc[r]);
         }
       }
+    }
+    if (EPI == 2) {
+      float v[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) v[r] = warp_sum(acc[r]);
+#pragma unroll
+      for (int r = 0; r < 4; r += 2) {
+        const int n = n0 + rg * 4 + r;
+        if (lane == 0 && n + 1 < N)
+          reinterpret_cast<__nv_bfloat16*>(C)[(size_t)pair * ldc + n / 2] = __float2bfloat16_rn(v[r] / (1.f + expf(-v[r])) * v[r + 1]);
+      }
+      continue;
     }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
@@ -374,8 +417,11 @@ using namespace vob;
 
 VOB_API int vob_moe_row_tile() { return MOE_TM; }
 
+// correction may be null; sigmoid_scores: scores are sigmoid(z), not the softmax; group_top 2: a group counts by its two best;
+// normalise: the chosen scores are divided by their sum; weight_scale: a factor on the weights.
 VOB_API int vob_moe_route(const void* h, const float* w_router, const float* correction, int* ids, float* weights, int T, int W,
-                          int E, int top, int count, int keep, int dtype, cudaStream_t stream) {
+                          int E, int top, int count, int keep, int sigmoid_scores, int group_top, int normalise,
+                          float weight_scale, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || count <= 0 || E % count || keep <= 0 || keep > count || (long)(E / count) * keep < top)
     return VOB_BAD_ARGUMENT;
@@ -386,7 +432,7 @@ VOB_API int vob_moe_route(const void* h, const float* w_router, const float* cor
     if (smem > 48 * 1024)                                                                                                \
       cudaFuncSetAttribute(moe_route_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
     return launch_kernel(moe_route_kernel<TYPE>, dim3(T), ROUTE_NT, smem, stream, (const TYPE*)h, w_router, correction, ids, \
-                         weights, W, E, top, count, keep);                                                               \
+                         weights, W, E, top, count, keep, sigmoid_scores, group_top, normalise, weight_scale);          \
   } while (0)
   if (dtype == VOB_F32) VOB_ROUTE(float);
   if (dtype == VOB_BF16) VOB_ROUTE(__nv_bfloat16);
@@ -403,7 +449,8 @@ VOB_API int vob_moe_align(const int* ids, int* slot_of, int* row_token, int* til
 }
 
 // A: rows of lda elements (`gather`: indexed by the row's token); W [experts, N, K]; C [max_rows, ldc] of `dtype`, or float
-// with `c_float`.  epilogue 0: as it is, 1: squared relu.
+// with `c_float`.  epilogue 0: as it is, 1: squared relu, 2: SiLU(gate) * up over rows of W in (gate, up) pairs: C has N / 2
+// columns.
 VOB_API int vob_moe_gemm(const void* A, long lda, const void* W, void* C, long ldc, const int* row_token, const int* tile_expert,
                          int max_rows, int N, int K, int epilogue, int gather, int c_float, int dtype, cudaStream_t stream) {
   if (max_rows <= 0 || N <= 0) return 0;
@@ -415,6 +462,7 @@ VOB_API int vob_moe_gemm(const void* A, long lda, const void* W, void* C, long l
                        row_token, tile_expert, N, K)
 #define VOB_MG_TYPE(TA)                                                   \
   if (epilogue == 1 && gather && !c_float) VOB_MG(TA, TA, 1, true);       \
+  if (epilogue == 2 && gather && !c_float) VOB_MG(TA, TA, 2, true);       \
   if (epilogue == 0 && !gather && c_float) VOB_MG(TA, float, 0, false);   \
   return VOB_UNSUPPORTED
   if (dtype == VOB_F32) { VOB_MG_TYPE(float); }
@@ -431,9 +479,10 @@ VOB_API int vob_moe_order(const int* ids, int* order, int n, int E, cudaStream_t
 }
 
 // A: bfloat16 rows of lda elements, a token's (`by_token`) or a pair's; W bfloat16 [experts, N, K], K a multiple of 8;
-// C [pairs, ldc]: bfloat16 with the squared relu (`relu2`) or float.  order: the pairs by expert (vob_moe_order).
+// C [pairs, ldc]: bfloat16 with the squared relu (`epilogue` 1) or with SiLU(gate) * up over rows of W in (gate, up) pairs
+// (2: N / 2 columns), or float (0).  order: the pairs by expert (vob_moe_order).
 VOB_API int vob_moe_gemv(const void* A, long lda, const void* W, void* C, long ldc, const int* ids, const int* order, int n,
-                         int top, int N, int K, int relu2, int by_token, cudaStream_t stream) {
+                         int top, int N, int K, int epilogue, int by_token, cudaStream_t stream) {
   if (n <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || (lda * 2) % 16 || ((uintptr_t)A | (uintptr_t)W) % 16 || n > 65535) return VOB_UNSUPPORTED;
   const size_t smem = (size_t)K * 2;
@@ -445,8 +494,9 @@ VOB_API int vob_moe_gemv(const void* A, long lda, const void* W, void* C, long l
     return launch_kernel(moe_gemv_kernel<EPI, BT>, grid, 256, smem, stream, (const __nv_bfloat16*)A, lda,                   \
                          (const __nv_bfloat16*)W, C, ldc, ids, order, top, N, K);                                          \
   } while (0)
-  if (relu2 && by_token) VOB_MV(1, true);
-  if (!relu2 && !by_token) VOB_MV(0, false);
+  if (epilogue == 1 && by_token) VOB_MV(1, true);
+  if (epilogue == 2 && by_token && N % 2 == 0) VOB_MV(2, true);
+  if (epilogue == 0 && !by_token) VOB_MV(0, false);
 #undef VOB_MV
   return VOB_UNSUPPORTED;
 }

@@ -12,8 +12,9 @@
 //   warp 1      allocates tensor memory (two accumulators) and issues the MMAs: four tcgen05.mma (K = 16 each) per stage;
 //               tcgen05.commit hands a stage back to the producer and, after an item's last, the accumulator to the epilogue;
 //   warps 2-5   epilogue: tcgen05.ld brings the accumulator to registers (a thread owns one output feature for all rows of
-//               the tile), applies f (identity into float, or the squared relu into bfloat16) and stores the rows that
-//               name a token; the next item's MMAs run meanwhile into the other accumulator.
+//               the tile), applies f (identity into float, the squared relu into bfloat16, or, rows of W in (gate, up)
+//               pairs, SiLU(gate) * up into bfloat16 feature / 2: the up value comes from the neighbouring lane) and stores
+//               the rows that name a token; the next item's MMAs run meanwhile into the other accumulator.
 // Which items exist is only known on the device (the sorting kernel ran just before), so nothing is copied before the wait
 // for the kernels ahead.  Every wait on an mbarrier is bounded; on a timeout the block sets an error bit, stops issuing
 // work, and still frees its tensor memory before it returns.
@@ -32,7 +33,7 @@ constexpr int MT_S = 6;
 constexpr int MT_NUM_BARRIERS = 2 * MT_S + 4;
 constexpr int MT_SMEM = 1024 + MT_S * MT_STAGE_BYTES + MT_NUM_BARRIERS * 8 + 16;
 
-enum { MT_EPI_RELU2_BF16 = 0, MT_EPI_F32 = 1 };
+enum { MT_EPI_RELU2_BF16 = 0, MT_EPI_F32 = 1, MT_EPI_SILU_PAIRS_BF16 = 2 };
 
 // tmW: W [experts * N, K] as 2-D map with box [128 rows, 64 columns]; tmX: the sorted rows [max_rows, K], same box.
 // tile_expert: one entry per 64 rows (the sorting kernel's granularity); row_token: one per row, -1 for padding.
@@ -153,6 +154,15 @@ moe_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const bool live = __shfl_sync(0xffffffffu, tok, j) >= 0;
+          if (EPI == MT_EPI_SILU_PAIRS_BF16) {
+            if (!live) continue;                                  // the same for every lane of the warp
+            const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
+            if (!(lane & 1) && n + 1 < N) {
+              const long m = (long)mt * MT_NT + c0 + j;
+              reinterpret_cast<__nv_bfloat16*>(out)[m * ldo + n / 2] = __float2bfloat16_rn(v[j] / (1.f + __expf(-v[j])) * up);
+            }
+            continue;
+          }
           if (live && n < N) {
             const long m = (long)mt * MT_NT + c0 + j;
             if (EPI == MT_EPI_F32) {
@@ -199,7 +209,8 @@ using namespace vob;
 VOB_API int vob_moe_tc5_row_tile() { return MT_NT; }
 
 // map_w: tensor map of W [experts * N, K] with box 128 rows; map_x: tensor map of the sorted rows [max_rows, K] with box 128
-// rows (vob_tensor_map_bf16_2d).  out [max_rows, ldo]: bfloat16 with the squared relu (epilogue 0) or float (1).
+// rows (vob_tensor_map_bf16_2d).  out [max_rows, ldo]: bfloat16 with the squared relu (epilogue 0), float (1), or bfloat16
+// SiLU(gate) * up over rows of W in (gate, up) pairs (2: N / 2 columns).
 VOB_API int vob_moe_gemm_tc5(const void* map_w, const void* map_x, void* out, long ldo, const int* row_token,
                              const int* tile_expert, int max_rows, int N, int K, int epilogue, int* err, cudaStream_t stream) {
   if (max_rows <= 0 || N <= 0) return 0;
@@ -207,7 +218,7 @@ VOB_API int vob_moe_gemm_tc5(const void* map_w, const void* map_x, void* out, lo
   const int row_tiles = max_rows / MT_NT;
   const long total = (long)row_tiles * ((N + MT_ROWS - 1) / MT_ROWS);
   const int blocks = (int)(total < sm_count() ? total : sm_count());
-  static bool configured[2] = {false, false};
+  static bool configured[3] = {false, false, false};
 #define VOB_MT(EPI)                                                                                                        \
   do {                                                                                                                     \
     if (!configured[EPI]) {                                                                                                \
@@ -220,6 +231,7 @@ VOB_API int vob_moe_gemm_tc5(const void* map_w, const void* map_x, void* out, lo
   } while (0)
   if (epilogue == MT_EPI_RELU2_BF16) VOB_MT(MT_EPI_RELU2_BF16);
   if (epilogue == MT_EPI_F32) VOB_MT(MT_EPI_F32);
+  if (epilogue == MT_EPI_SILU_PAIRS_BF16 && N % 2 == 0) VOB_MT(MT_EPI_SILU_PAIRS_BF16);
 #undef VOB_MT
   return VOB_BAD_ARGUMENT;
 }

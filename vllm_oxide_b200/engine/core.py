@@ -36,6 +36,7 @@ class StepContext:
         self.launch_requests = L.B
         self.next_norm = None      # hints between blocks within a step (models/causal_lm.py sets them, parts/block.py reads them)
         self.prenormed = None
+        self.pending_second = None  # a second output that waits beside `hidden` for the stream (parts/parallel.py)
         self.reinject = False      # the run that comes next adds the embedding's output back (models/plan.py: ExecStep.reinject)
         self.token_ids = dev[L.token_ids:L.token_ids + L.T]
         self.positions = dev[L.positions:L.positions + L.T]

@@ -204,21 +204,89 @@ def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, rule, kcache, vca
 
 def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, token_req, positions, num_tokens, nh, kvh,
                             hd, window: int, scale: float, err, skip_single_cu_q=None, value_dim: Optional[int] = None,
-                            sink: bool = False, gate=None, gate_stride: int = 0) -> None:
+                            sink: bool = False, gate=None, gate_stride: int = 0, softcap: float = 0.0, chunk: int = 0) -> None:
     """Every token of the batch; with `skip_single_cu_q` (the batch's cu_q) the tokens of requests that
     bring exactly one token are left to the decode kernel.  `value_dim`: only that many leading elements of a value
     row are read and `out` is [tokens, nh * value_dim] (keys and values may then be one and the same plane).
     `sink`: the softmax has a silent extra entry of score 0; `gate` (a view whose element [t * gate_stride + h] is head
-    h's number for token t): every head's output is multiplied by the sigmoid of its number."""
+    h's number for token t): every head's output is multiplied by the sigmoid of its number.  A value plane
+    [pages, value heads, page size, value size] of another shape than the key plane is read by its own shape (neighbouring
+    key heads share a value head) and `out` is [tokens, nh * value size]; `softcap` > 0: scores become softcap *
+    tanh(score / softcap); `chunk` > 0: a query sees only keys of its own block of `chunk` positions; a float32 `out`
+    beside bfloat16 inputs is stored unrounded."""
     _cuda(q, out, kcache, vcache, block_tables, token_req, positions, gate)
     assert gate is None or gate.dtype == q.dtype
+    own_shape = vcache.shape[1] != kcache.shape[1] or vcache.shape[3] != kcache.shape[3]
+    if own_shape:
+        assert value_dim is None or value_dim == vcache.shape[3]
+        value_dim = vcache.shape[3]
+    assert vcache.shape[0] == kcache.shape[0] and vcache.shape[2] == kcache.shape[2]
+    assert out.dtype in (q.dtype, torch.float32)
     _check(lib().vob_paged_attention_generic(_p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache),
                                              _p(block_tables), block_tables.shape[-1], _p(token_req), _p(positions),
                                              _p(skip_single_cu_q), num_tokens, nh, kvh, hd,
                                              hd if value_dim is None else int(value_dim), kcache.shape[2], window,
                                              ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), int(bool(sink)), _p(gate),
-                                             ctypes.c_long(gate_stride), _code(q.dtype), _p(err), _stream()),
+                                             ctypes.c_long(gate_stride), vcache.shape[1], vcache.shape[3],
+                                             ctypes.c_float(softcap), int(chunk), int(out.dtype != q.dtype), _code(q.dtype),
+                                             _p(err), _stream()),
            "paged_attention_generic")
+
+
+def rownorm_rope_kv_write(qkv, positions, slots, wq, wk, rule, kcache, vcache, num_tokens: int, nh: int, kvh: int, kd: int,
+                          eps: float, write_kv: bool, err) -> None:
+    """A merged q|k|v row whose keys and values have shapes of their own: q (all heads at once) and k each pass an RMS norm
+    with a gain (wq, wk float, both or neither), the front of every q and k head turns by computed angles (`rule` with
+    `frequencies`; rotary_dim 0 turns nothing), q is written back in place, k goes to `kcache` [pages, kvh, page size, kd]
+    and v as projected to `vcache` [pages, value heads, page size, value size]."""
+    _cuda(qkv, positions, slots, wq, wk, rule.frequencies, kcache, vcache)
+    if rule.rotary_dim > 0 and (rule.frequencies is None or rule.amplitude != 1.0):
+        raise KernelError("rownorm_rope_kv_write turns by computed angles: the rule needs `frequencies` and amplitude 1")
+    assert qkv.stride(1) == 1 and kcache.dtype == qkv.dtype == vcache.dtype and tuple(kcache.shape[1::2]) == (kvh, kd)
+    assert kcache.shape[0] == vcache.shape[0] and kcache.shape[2] == vcache.shape[2]
+    for w in (wq, wk):
+        assert w is None or (w.dtype == torch.float32 and w.is_contiguous())
+    _check(lib().vob_rownorm_rope_kv_write(_p(qkv), ctypes.c_long(qkv.stride(0)), _p(positions), _p(slots), _p(wq), _p(wk),
+                                           _p(rule.frequencies), _p(kcache), _p(vcache), num_tokens, nh, kvh, kd,
+                                           vcache.shape[1], vcache.shape[3], rule.rotary_dim, int(rule.interleaved),
+                                           ctypes.c_float(eps), ctypes.c_long(kcache.shape[0] * kcache.shape[2]),
+                                           kcache.shape[2], int(write_kv), _code(qkv.dtype), _p(err), _stream()),
+           "rownorm_rope_kv_write")
+
+
+def diff_heads_combine(a, gate, gate_stride: int, out, num_tokens: int, heads: int, group: int, vd: int, lam: float, post: float,
+                       eps: float) -> None:
+    """out[t, h] = (a1 - lam * a2) / sqrt(mean((a1 - lam * a2)^2) + eps) * post * sigmoid(gate[t, h]) for heads that are
+    two maps: `a` [tokens, 2 * heads * vd] (float32, or out's type) holds, per key/value head, the first maps of its
+    `group` heads and then their second maps; `gate` (None: none): a view with rows `gate_stride` apart, heads * vd numbers
+    a token; `out` [tokens, heads * vd] in the heads' own order."""
+    _cuda(a, gate, out)
+    assert a.is_contiguous() and out.is_contiguous() and a.dtype in (out.dtype, torch.float32)
+    assert gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1)
+    _check(lib().vob_diff_heads_combine(_p(a), int(a.dtype == torch.float32), _p(gate), ctypes.c_long(gate_stride), _p(out),
+                                        num_tokens, heads, group, vd, ctypes.c_float(lam), ctypes.c_float(post),
+                                        ctypes.c_float(eps), _code(out.dtype), _stream()), "diff_heads_combine")
+
+
+def layer_norm_step(stream, eps: float, err, y1=None, y2=None, w=None, b=None, out=None, rows=None, n_out: Optional[int] = None,
+                    init: bool = False) -> None:
+    """One pass over a float residual stream [tokens, width] around layers whose sublayers share one norm: x = 0 (`init`)
+    or the stream's row; x += (y1 + y2); the row is stored; out = LayerNorm(x) * w + b (mean and variance of the row, the
+    variance as the mean of squared deviations).  With `rows` (source rows, `n_out` of them) only `out` is computed and
+    nothing is stored."""
+    _cuda(stream, y1, y2, w, b, out, rows)
+    assert stream.dtype == torch.float32 and stream.is_contiguous()
+    for t in (w, b):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    act = next((t for t in (out, y1, y2) if t is not None), None)
+    for t in (y1, y2, out):
+        assert t is None or (t.dtype == act.dtype and t.is_contiguous() and t.shape[1] == stream.shape[1])
+    n_src = stream.shape[0]
+    n = n_src if rows is None else int(n_out)
+    _check(lib().vob_layer_norm_step(_p(stream), _p(y1), _p(y2), _p(w), _p(b), _p(out), _p(rows), n, n_src, stream.shape[1],
+                                     ctypes.c_float(eps), int(bool(init)),
+                                     _code(act.dtype if act is not None else torch.float32), _p(err), _stream()),
+           "layer_norm_step")
 
 
 def rope_shared_kv_write(qk, positions, slots, rule, kcache, vcache, num_tokens: int, nh: int, kvh: int, hd: int,
@@ -320,13 +388,19 @@ def moe_row_tile() -> int:
     return int(lib().vob_moe_row_tile())
 
 
-def moe_route(h, w_router, correction, ids, weights, num_tokens: int, top: int, groups: int, keep: int) -> None:
-    """ids, weights [tokens, top]: the experts a token uses and their softmax scores (see csrc/kernels/moe.cu)."""
+def moe_route(h, w_router, correction, ids, weights, num_tokens: int, top: int, groups: int, keep: int,
+              sigmoid_scores: bool = False, group_top: int = 1, normalise: bool = False, weight_scale: float = 1.0) -> None:
+    """ids, weights [tokens, top]: the experts a token uses and their scores (see csrc/kernels/moe.cu): the softmax over
+    all experts or (`sigmoid_scores`) a sigmoid each, chosen by score + `correction` (None: by the score) among the `keep`
+    groups that count most, a group by its best choice score or (`group_top` 2) by the sum of its two best; the weights
+    are the chosen scores, divided by their sum with `normalise`, times `weight_scale`."""
     _cuda(h, w_router, correction, ids, weights)
     E, W = w_router.shape
-    assert h.is_contiguous() and h.shape[1] == W and w_router.dtype == correction.dtype == torch.float32
-    assert w_router.is_contiguous() and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    assert h.is_contiguous() and h.shape[1] == W and w_router.dtype == torch.float32
+    assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous())
+    assert w_router.is_contiguous() and ids.dtype == torch.int32 and weights.dtype == torch.float32 and group_top in (1, 2)
     _check(lib().vob_moe_route(_p(h), _p(w_router), _p(correction), _p(ids), _p(weights), num_tokens, W, E, top, groups, keep,
+                               int(bool(sigmoid_scores)), int(group_top), int(bool(normalise)), ctypes.c_float(weight_scale),
                                _code(h.dtype), _stream()), "moe_route")
 
 
@@ -349,16 +423,17 @@ def moe_gemm_tc5_supported(a, w) -> bool:
             and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def moe_gemm_tc5(a, w, c, row_token, tile_expert, relu_squared: bool, err) -> None:
+def moe_gemm_tc5(a, w, c, row_token, tile_expert, relu_squared: bool, err, silu_pairs: bool = False) -> None:
     """c[row] = f(a[row] @ w[expert of the row]^T) on the tcgen05 tensor cores: a [rows, K] bfloat16 already sorted by
-    expert in row tiles of moe_tc5_row_tile(), w [experts, N, K]; c bfloat16 with the squared relu, or float."""
+    expert in row tiles of moe_tc5_row_tile(), w [experts, N, K]; c bfloat16 with the squared relu, bfloat16 [rows, N / 2]
+    with `silu_pairs` (rows of w in (gate, up) pairs: SiLU(gate) * up), or float."""
     _cuda(a, w, c, row_token, tile_expert)
     E, N, K = w.shape
     assert moe_gemm_tc5_supported(a, w) and a.shape[0] == row_token.numel() and c.stride(1) == 1
-    assert c.dtype == (torch.bfloat16 if relu_squared else torch.float32)
+    assert c.dtype == (torch.bfloat16 if relu_squared or silu_pairs else torch.float32) and not (relu_squared and silu_pairs)
     map_w, map_x = tensor_map_2d(w.view(E * N, K), 128), tensor_map_2d(a, 128)
     _check(lib().vob_moe_gemm_tc5(map_w, map_x, _p(c), ctypes.c_long(c.stride(0)), _p(row_token), _p(tile_expert), a.shape[0], N, K,
-                                  0 if relu_squared else 1, _p(err), _stream()), "moe_gemm_tc5")
+                                  2 if silu_pairs else (0 if relu_squared else 1), _p(err), _stream()), "moe_gemm_tc5")
 
 
 def moe_gather_rows(x, xs, row_token) -> None:
@@ -369,14 +444,17 @@ def moe_gather_rows(x, xs, row_token) -> None:
                                      _stream()), "moe_gather_rows")
 
 
-def moe_gemm(a, w, c, row_token, tile_expert, relu_squared: bool, gather: bool) -> None:
-    """c[row] = f(a[row or its token] @ w[expert of the row]^T), w [experts, N, K]; float accumulation in one chain."""
+def moe_gemm(a, w, c, row_token, tile_expert, relu_squared: bool, gather: bool, silu_pairs: bool = False) -> None:
+    """c[row] = f(a[row or its token] @ w[expert of the row]^T), w [experts, N, K]; float accumulation in one chain.  f: the
+    squared relu, or (`silu_pairs`: rows of w in (gate, up) pairs, c [rows, N / 2]) SiLU(gate) * up, both with `gather`
+    into a's type; or the identity into float."""
     _cuda(a, w, c, row_token, tile_expert)
     assert a.stride(1) == 1 and w.is_contiguous() and c.stride(1) == 1 and a.dtype == w.dtype
-    assert c.dtype == (a.dtype if relu_squared else torch.float32) and relu_squared == gather
+    first = relu_squared or silu_pairs
+    assert c.dtype == (a.dtype if first else torch.float32) and first == gather and not (relu_squared and silu_pairs)
     _check(lib().vob_moe_gemm(_p(a), ctypes.c_long(a.stride(0)), _p(w), _p(c), ctypes.c_long(c.stride(0)), _p(row_token),
-                              _p(tile_expert), row_token.numel(), w.shape[1], w.shape[2], int(relu_squared), int(gather),
-                              int(not relu_squared),
+                              _p(tile_expert), row_token.numel(), w.shape[1], w.shape[2], 2 if silu_pairs else int(relu_squared),
+                              int(gather), int(not first),
                               _code(a.dtype), _stream()), "moe_gemm")
 
 
@@ -392,14 +470,16 @@ def moe_gemv_supported(a, w, n: int) -> bool:
             and w.is_contiguous() and n <= 65535)
 
 
-def moe_gemv(a, w, c, ids, order, n: int, top: int, relu_squared: bool) -> None:
+def moe_gemv(a, w, c, ids, order, n: int, top: int, relu_squared: bool, silu_pairs: bool = False) -> None:
     """c[pair] = f(a[pair or its token] @ w[expert of the pair]^T) for the step's pairs, few of them (decoding): bfloat16,
     bound by the experts' rows, which a warp streams with 16-byte loads.  relu_squared: the first product (a by token, c
     bfloat16); else the second (a by pair, c float)."""
     _cuda(a, w, c, ids, order)
-    assert moe_gemv_supported(a, w, n) and c.stride(1) == 1 and c.dtype == (torch.bfloat16 if relu_squared else torch.float32)
+    first = relu_squared or silu_pairs          # silu_pairs: rows of w in (gate, up) pairs, c bfloat16 [pairs, N / 2]
+    assert moe_gemv_supported(a, w, n) and c.stride(1) == 1 and c.dtype == (torch.bfloat16 if first else torch.float32)
     _check(lib().vob_moe_gemv(_p(a), ctypes.c_long(a.stride(0)), _p(w), _p(c), ctypes.c_long(c.stride(0)), _p(ids), _p(order), n,
-                              top, w.shape[1], w.shape[2], int(relu_squared), int(relu_squared), _stream()), "moe_gemv")
+                              top, w.shape[1], w.shape[2], 2 if silu_pairs else int(relu_squared), int(first), _stream()),
+           "moe_gemv")
 
 
 def moe_combine(y, slot_of, weights, out, num_tokens: int, top: int) -> None:

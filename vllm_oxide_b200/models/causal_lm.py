@@ -122,7 +122,7 @@ class CausalLM:
         if self.embedding_norm is not None:
             hidden, residual = self.embedding_norm.open_stream(hidden, ctx, keep=self._reinjects)
         order = self.plan.order
-        ctx.prenormed = None
+        ctx.prenormed = ctx.pending_second = None
         for i, s in enumerate(order):
             ctx.reinject = s.reinject
             plane = self.planes[s.plane] if s.plane is not None else None

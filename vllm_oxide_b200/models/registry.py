@@ -7,10 +7,11 @@ from __future__ import annotations
 
 from typing import Callable, Dict, Tuple
 
-from ..config.model_config import ConfigError, KesozenConfig, Qwen3Config, TofilornConfig
+from ..config.model_config import ConfigError, KesozenConfig, Qwen3Config, RakizenConfig, TofilornConfig
 from .kesozen import kesozen_plan
 from .plan import ModelPlan
 from .qwen3 import qwen3_plan
+from .rakizen import rakizen_plan
 from .tofilorn import tofilorn_plan
 
 _ARCHITECTURES: Dict[str, Tuple[Callable[[dict], object], Callable[[object], ModelPlan]]] = {}
@@ -43,3 +44,4 @@ def resolve(config_dict: dict, where: str = "config.json"):
 register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict, qwen3_plan)
 register_architecture("Tofilorn", TofilornConfig.from_dict, tofilorn_plan)
 register_architecture("Kesozen", KesozenConfig.from_dict, kesozen_plan)
+register_architecture("Rakizen", RakizenConfig.from_dict, rakizen_plan)

@@ -204,21 +204,27 @@ class SharedKVAttention(Mixer):
 
 
 def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: int, kvh: int, hd: int, window: int,
-                 scale: float, pairs=None, value_dim=None, sink: bool = False, gate=None, gate_stride: int = 0) -> int:
+                 scale: float, pairs=None, value_dim=None, sink: bool = False, gate=None, gate_stride: int = 0,
+                 softcap: float = 0.0, chunk: int = 0) -> int:
     """Attention of every query of the step over the pages of `keys` / `values`; returns the width of a head in `out`.
     bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a portion to the
     tensor-core kernel for portions.  The 32-bit path, and sizes those kernels refuse, go to the plain kernel.
     `value_dim` (keys and values are one plane whose rows begin with the value): the plain kernel reads and writes only
     that much of a value row; the tensor-core kernels take whole rows, and the caller uses the first `value_dim`
     elements of each head of `out`.  `sink`: the softmax has a silent extra entry of score 0.  `gate`: a view whose element
-    [t, h] (rows `gate_stride` apart) is head h's gate of token t; its output is multiplied by the sigmoid of it."""
+    [t, h] (rows `gate_stride` apart) is head h's gate of token t; its output is multiplied by the sigmoid of it.
+    `softcap` > 0: scores become softcap * tanh(score / softcap); `chunk` > 0: a query sees only keys of its own block of
+    `chunk` positions.  Values of another shape than the keys (their own head size, or fewer heads) and a float `out`
+    beside 16-bit inputs go to the plain kernel."""
     tables = ctx.block_tables[group]
+    own_values = tuple(values.shape) != tuple(keys.shape)
     fast = kernels.has_fast_attention(q.dtype, hd, nh // kvh) and scale > 0.0      # the tcgen05 kernel takes maxima before it scales
+    fast = fast and not own_values and out.dtype == q.dtype and (FAST_CAP_AND_CHUNK or not (softcap or chunk))
     if not fast or ((sink or gate is not None) and not FAST_SINK_AND_GATE):
         kernels.paged_attention_generic(q, q_stride, out, keys, values, tables, ctx.token_req, ctx.positions, T,
                                         nh, kvh, hd, window, scale, ctx.err, value_dim=value_dim, sink=sink, gate=gate,
-                                        gate_stride=gate_stride)
-        return hd if value_dim is None else value_dim
+                                        gate_stride=gate_stride, softcap=softcap, chunk=chunk)
+        return values.shape[3] if own_values else (hd if value_dim is None else value_dim)
     B = ctx.launch_requests
     if ctx.num_decode > 0:
         n_keys = ctx.max_context if window == 0 else min(ctx.max_context, window)
@@ -236,6 +242,8 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
 
 # Whether the tensor-core attention kernels take a softmax with a sink and a gate on the heads (else the plain kernel does).
 FAST_SINK_AND_GATE = True
+# Whether they take capped scores and blocks of positions (else the plain kernel does).
+FAST_CAP_AND_CHUNK = False
 
 DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)
 

@@ -41,16 +41,30 @@ class CacheSpec:
     """What a mixer keeps in pages, a token: `tensors` tensors (2: keys and values; 1: a single tensor, e.g. a latent that
     stands for both) of `kv_heads * head_dim` elements each, for all positions (window 0) or the last `window`; in pages
     of `block_size` tokens (None: the engine's page size) and in `dtype` (None: the model's).  A plane is stored as
-    [tensors, pages, kv_heads, block_size, head_dim].  Planes with equal windows and page sizes share a group: one page
-    pool and one block table per request, whatever their widths, tensors and dtypes."""
+    [tensors, pages, kv_heads, block_size, head_dim].  With `value_heads` / `value_dim` the second tensor has a shape of
+    its own, [pages, value_heads, block_size, value_dim] (values wider or narrower than keys, or key heads that share a
+    value head), and the two tensors are allocated apart.  `chunk` > 0: queries read only keys of their own block of
+    `chunk` positions (blocks counted from position 0), so the pages of blocks that lie behind are given back, as those
+    a window has passed.  Planes with equal windows, chunks and page sizes share a group: one page pool and one block
+    table per request, whatever their widths, tensors and dtypes."""
     kv_heads: int
     head_dim: int
     window: int = 0
     tensors: int = 2
     block_size: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    value_heads: Optional[int] = None
+    value_dim: Optional[int] = None
+    chunk: int = 0
+
+    def value_shape(self) -> Tuple[int, int]:
+        """(heads, head size) of the second tensor."""
+        return (self.value_heads or self.kv_heads, self.value_dim or self.head_dim)
 
     def elements_per_token(self) -> int:
+        if self.tensors == 2:
+            vh, vd = self.value_shape()
+            return self.kv_heads * self.head_dim + vh * vd
         return self.tensors * self.kv_heads * self.head_dim
 
 
@@ -64,7 +78,8 @@ class StateSpec:
 @dataclass
 class CachePlane:
     """One layer's pages: `k` (the first, or only, tensor) and `v` (the second, None for a one-tensor plane), each
-    [num_pages, kv_heads, block_size, head_dim]; `data` is both as one tensor [tensors, num_pages, ...]."""
+    [num_pages, kv_heads, block_size, head_dim]; `data` is both as one tensor [tensors, num_pages, ...] (None when the
+    second tensor has a shape of its own: `v` is then [num_pages, value_heads, block_size, value_dim])."""
     k: torch.Tensor
     v: Optional[torch.Tensor]
     group: int

@@ -1,4 +1,4 @@
-"""Feed-forwards with the squared relu: a dense one, and a mixture of experts chosen among groups.
+"""A dense feed-forward with the squared relu, and a mixture of experts chosen among groups.
 
 `ReluSquaredMLP`: down(max(up(x), 0)^2).
 
@@ -10,6 +10,12 @@ plain scores s, not renormalised, and the output is the weighted sum of their ou
 experts: the step's (token, choice) pairs are sorted by expert on the device, the experts' products run over the sorted
 rows (each expert's rows padded to a row tile), and a last kernel sums a token's rows in order.  No count leaves the
 device, so a step launches the same kernels whatever the router decides.
+
+Options of `RoutedExperts`, for designs that route otherwise: `activation` "silu_gated" makes an expert
+down(SiLU(gate(x)) * up(x)) (<prefix>e<i>.gate beside up and down; gate and up rows are stored in pairs so that the
+activation is the epilogue of ONE product); `scores` "sigmoid" takes s = sigmoid(z) instead of the softmax; `correction`
+False has no correction tensor (the choice is by s); `group_top` 2 lets a group count by the sum of its two best choice
+scores; `normalise` divides the chosen scores by their sum (+ 1e-20); `weight_scale` multiplies them.
 """
 from __future__ import annotations
 
@@ -54,12 +60,19 @@ class RoutedExperts(FeedForward):
     graph_safe = True
 
     def __init__(self, hidden_size: int, expert_size: int, experts: int, top: int, prefix: str, groups: int = 1, keep: int = 1,
-                 names=("up", "down", "router", "correction"), **_):
+                 names=("up", "down", "router", "correction"), activation: str = "relu2", gate_name: str = "gate",
+                 scores: str = "softmax", correction: bool = True, group_top: int = 1, normalise: bool = False,
+                 weight_scale: float = 1.0, **_):
         self.H, self.I, self.E, self.top = int(hidden_size), int(expert_size), int(experts), int(top)
         self.groups, self.keep, self.prefix = int(groups), int(keep), prefix
         if self.E % self.groups or self.keep > self.groups or self.top > (self.E // self.groups) * self.keep:
             raise ValueError(f"{self.E} experts in {self.groups} groups of which {self.keep} are kept cannot give {self.top} choices")
+        if activation not in ("relu2", "silu_gated") or scores not in ("softmax", "sigmoid") or group_top not in (1, 2):
+            raise ValueError(f"unknown choice among activation {activation!r}, scores {scores!r}, group_top {group_top!r}")
         self.n_up, self.n_down, self.n_router, self.n_correction = names
+        self.n_gate, self.gated = gate_name, activation == "silu_gated"
+        self.sigmoid_scores, self.has_correction, self.group_top = scores == "sigmoid", bool(correction), int(group_top)
+        self.normalise, self.weight_scale = bool(normalise), float(weight_scale)
         self.wup = self.wdown = self.router = self.correction = None
 
     def _expert(self, e: int, name: str) -> str:
@@ -68,16 +81,30 @@ class RoutedExperts(FeedForward):
     def tensor_specs(self) -> List[TensorSpec]:
         specs = []
         for e in range(self.E):
+            if self.gated:
+                specs.append(TensorSpec(self._expert(e, self.n_gate), (self.I, self.H), "matrix", self.H))
             specs += [TensorSpec(self._expert(e, self.n_up), (self.I, self.H), "matrix", self.H),
                       TensorSpec(self._expert(e, self.n_down), (self.H, self.I), "matrix", self.I)]
-        return specs + [TensorSpec(self.prefix + self.n_router, (self.E, self.H), "coefficient", self.H, init="normal"),
-                        TensorSpec(self.prefix + self.n_correction, (self.E,), "coefficient", init="small")]
+        specs.append(TensorSpec(self.prefix + self.n_router, (self.E, self.H), "coefficient", self.H, init="normal"))
+        if self.has_correction:
+            specs.append(TensorSpec(self.prefix + self.n_correction, (self.E,), "coefficient", init="small"))
+        return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.wup = torch.stack([tensors[self._expert(e, self.n_up)] for e in range(self.E)]).contiguous()
+        up = torch.stack([tensors[self._expert(e, self.n_up)] for e in range(self.E)])
+        if self.gated:
+            # rows in pairs (gate row, up row of the same output): the activation becomes the first product's epilogue
+            gate = torch.stack([tensors[self._expert(e, self.n_gate)] for e in range(self.E)])
+            up = torch.stack([gate, up], dim=2).reshape(self.E, 2 * self.I, self.H)
+        self.wup = up.contiguous()
         self.wdown = torch.stack([tensors[self._expert(e, self.n_down)] for e in range(self.E)]).contiguous()
         self.router = tensors[self.prefix + self.n_router].contiguous()
-        self.correction = tensors[self.prefix + self.n_correction].contiguous()
+        self.correction = tensors[self.prefix + self.n_correction].contiguous() if self.has_correction else None
+
+    def _route(self, x, ids, weights, T: int) -> None:
+        kernels.moe_route(x, self.router, self.correction, ids, weights, T, self.top, self.groups, self.keep,
+                          sigmoid_scores=self.sigmoid_scores, group_top=self.group_top, normalise=self.normalise,
+                          weight_scale=self.weight_scale)
 
     def forward(self, x, ctx):
         T, top = x.shape[0], self.top
@@ -90,10 +117,10 @@ class RoutedExperts(FeedForward):
             # bfloat16 steps of few pairs (decoding): nothing is sorted into tiles; the pairs are listed by expert and each
             # streams its expert's rows
             order = ctx.ws.get_flat("moe_order", n, torch.int32)
-            kernels.moe_route(x, self.router, self.correction, ids, weights, T, top, self.groups, self.keep)
+            self._route(x, ids, weights, T)
             kernels.moe_order(ids, order, n, self.E)
             act = ctx.ws.get_flat("moe_act", n * self.I, x.dtype).view(n, self.I)
-            kernels.moe_gemv(x, self.wup, act, ids, order, n, top, True)
+            kernels.moe_gemv(x, self.wup, act, ids, order, n, top, not self.gated, silu_pairs=self.gated)
             y = ctx.ws.get_flat("moe_y", n * self.H, torch.float32).view(n, self.H)
             kernels.moe_gemv(act, self.wdown, y, ids, order, n, top, False)
             out = ctx.ws.get("mlp_out", T, self.H, x.dtype)
@@ -105,17 +132,18 @@ class RoutedExperts(FeedForward):
         slot_of = ctx.ws.get_flat("moe_slot_of", n, torch.int32)
         row_token = ctx.ws.get_flat("moe_row_token", max_rows, torch.int32)
         tile_expert = ctx.ws.get_flat("moe_tile_expert", max_rows // kernels.moe_row_tile(), torch.int32)
-        kernels.moe_route(x, self.router, self.correction, ids, weights, T, top, self.groups, self.keep)
+        self._route(x, ids, weights, T)
         kernels.moe_align(ids, slot_of, row_token, tile_expert, n, top, self.E, pad=tile)
         act = ctx.ws.get_flat("moe_act", max_rows * self.I, x.dtype).view(max_rows, self.I)
         y = ctx.ws.get_flat("moe_y", max_rows * self.H, torch.float32).view(max_rows, self.H)
         if fast:
             rows = ctx.ws.get_flat("moe_rows", max_rows * self.H, x.dtype).view(max_rows, self.H)
             kernels.moe_gather_rows(x, rows, row_token)
-            kernels.moe_gemm_tc5(rows, self.wup, act, row_token, tile_expert, True, ctx.err)
+            kernels.moe_gemm_tc5(rows, self.wup, act, row_token, tile_expert, not self.gated, ctx.err, silu_pairs=self.gated)
             kernels.moe_gemm_tc5(act, self.wdown, y, row_token, tile_expert, False, ctx.err)
         else:
-            kernels.moe_gemm(x, self.wup, act, row_token, tile_expert, relu_squared=True, gather=True)
+            kernels.moe_gemm(x, self.wup, act, row_token, tile_expert, relu_squared=not self.gated, gather=True,
+                             silu_pairs=self.gated)
             kernels.moe_gemm(act, self.wdown, y, row_token, tile_expert, relu_squared=False, gather=False)
         out = ctx.ws.get("mlp_out", T, self.H, x.dtype)
         kernels.moe_combine(y, slot_of, weights, out, T, top)
