@@ -18,10 +18,12 @@ of 8 requests whose context starts at 2,048 tokens, and prints ONE JSON line:
 The cache that the decode steps read was written by a real prefill of random prompts.  Every timed step reads 15 GB of weights, far more than the 126 MB L2, so nothing stays cached
 between iterations.  Peaks come from MEASURED_PEAKS.json beside this file when present.
 
-    python bench.py --workload tofilorn | kesozen [--sizes 2048,4096]
+    python bench.py --workload tofilorn | kesozen | rakizen [--sizes 2048,4096]
 
-measures the Tofilorn design (residual streams, minGRU, HGRN2, latent attention) or the Kesozen design (sandwich norms over
-a float stream, attention whose keys are its values, gated delta rule, routed experts) at layer sizes of 1B- and 8B-class
+measures the Tofilorn design (residual streams, minGRU, HGRN2, latent attention), the Kesozen design (sandwich norms over
+a float stream, attention whose keys are its values, gated delta rule, routed experts) or the Rakizen design (parallel
+layers over a float stream, capped scores, two-map heads over blocks of positions, sliding windows, gated experts; also
+beside Kesozen, with attention held against arithmetic in prompts and against the keys and values read in decoding) at layer sizes of 1B- and 8B-class
 models beside Qwen3 at the same width, depth and feed-forward size (Kesozen also beside Tofilorn): one 2,048-token prompt in one step, decode at batch 8
 and 64 from a 2,048-token context (CUDA graphs), and, from an eager engine with the per-kernel timers on, the time of each
 of this package's kernels in those steps with the bytes it must move against the copy bandwidth.
@@ -417,6 +419,83 @@ def kesozen_kernel_bytes(cfg: dict, T: int) -> dict:
     return b
 
 
+def rakizen_config(width: int, layers: int) -> dict:
+    """Layer sizes of a real model of this width: a block of four layers (two-map attention over blocks of 1,536 positions,
+    two sliding windows of 1,024 with half of every head rotated, two-map attention again), heads of 128 with 8 key heads
+    (the two-map layers hold two key maps a key head); feed-forwards of 16 gated experts of which a token uses 4 (the four
+    together three times the width), but for the second layer of each block, whose feed-forward is dense and three times
+    the width."""
+    heads = width // 128
+    two = dict(heads=heads, kv_heads=8, dim=128, vdim=128, diff=0.3, scale=128 ** -0.5, softcap=30.0, mask={"size": 1536})
+    win = dict(heads=heads, kv_heads=8, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0, mask={"size": 1024},
+               rot={"dims": 64, "base": 10000.0})
+    moe = {"kind": "moe", "expert": {"ff": 3 * width // 4}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2},
+                                                                     "scale": 2.0}}
+    dense = {"kind": "dense", "ff": 3 * width}
+    out = []
+    for _ in range(0, layers, 4):
+        out += [{"type": "attention", "mixer": two, "mlp": moe}, {"type": "attention_2", "mixer": win, "mlp": dense},
+                {"type": "attention_2", "mixer": win, "mlp": moe}, {"type": "attention", "mixer": two, "mlp": moe}]
+    return {"architecture": "Rakizen", "vocab": 32768, "width": width, "norm": {"eps": 1e-6}, "layers": out[:layers]}
+
+
+def rakizen_kernel_bytes(cfg: dict, T: int) -> dict:
+    """Bytes that each of the design's own row-wise kernels must move in a step of T tokens, summed over the layers (weights
+    aside): what its time is held against.  Attention and the experts' products are held against arithmetic instead."""
+    D = cfg["width"]
+    b = {"layer_norm_step": T * (D * 2 + D * 4 + D * 2)}                          # the stream begins: tokens in, stream and normed out
+    for l in cfg["layers"]:
+        m, mlp = l["mixer"], l["mlp"]
+        maps = 2 if l["type"] == "attention" else 1
+        nh, kvh, d, e = maps * m["heads"], maps * m["kv_heads"], m["dim"], m["vdim"]
+        b["layer_norm_step"] += T * (2 * D * 4 + (3 if mlp else 2) * D * 2)       # stream read and written, outputs in, normed out
+        # q and k read and written back, v read; k and v written to the cache
+        b["rownorm_rope_kv_write"] = b.get("rownorm_rope_kv_write", 0) + T * (2 * (nh + kvh) * d + 2 * m["kv_heads"] * e + kvh * d) * 2
+        if maps == 2:
+            b["diff_heads_combine"] = b.get("diff_heads_combine", 0) + T * m["heads"] * e * (2 * 4 + 2 + 2)
+        if mlp and mlp["kind"] == "dense":
+            b["silu_mul"] = b.get("silu_mul", 0) + T * 3 * mlp["ff"] * 2
+        elif mlp:
+            top = mlp["router"]["top"]
+            b["moe_gather_rows"] = b.get("moe_gather_rows", 0) + T * top * D * 2 * 2
+            b["moe_combine"] = b.get("moe_combine", 0) + T * (top * D * 4 + D * 2)
+    return b
+
+
+def attention_flops(cfg: dict, T: int) -> float:
+    """Multiply-adds x 2 of the score and value products of one prompt of T tokens, every query over the keys it sees."""
+    def seen(size, blocks):
+        if not size:
+            return T * (T + 1) // 2
+        return sum((i % size if blocks else min(i, size - 1)) + 1 for i in range(T))
+    if "layers" not in cfg:
+        return cfg["num_hidden_layers"] * 4.0 * cfg["num_attention_heads"] * cfg["head_dim"] * seen(0, False)
+    total = 0.0
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        if l["type"] in ("attention", "attention_2") and "dim" in m:
+            maps = 2 if (l["type"] == "attention" and "diff" in m) else 1
+            size = (m.get("mask") or {}).get("size", 0)
+            total += 2.0 * maps * m["heads"] * (m["dim"] + m["vdim"]) * seen(size, maps == 2)
+    return total
+
+
+def attention_decode_bytes(cfg: dict, batch: int, context: int) -> float:
+    """Bytes of keys and values that one decode step of `batch` requests at `context` tokens must read (bfloat16)."""
+    if "layers" not in cfg:
+        return cfg["num_hidden_layers"] * batch * context * 2.0 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+    total = 0.0
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        if l["type"] in ("attention", "attention_2") and "dim" in m:
+            two = l["type"] == "attention" and "diff" in m
+            size = (m.get("mask") or {}).get("size", 0)
+            keys = context if not size else (context % size + 1 if two else min(context, size))
+            planes = m["dim"] if cfg["architecture"] == "Kesozen" else (2 if two else 1) * m["dim"] + m["vdim"]   # Kesozen: keys are values
+            total += batch * keys * m["kv_heads"] * planes * 2.0
+    return total
+
+
 def qwen3_kernel_bytes(cfg: dict, T: int) -> dict:
     """The same for the row-wise kernels of a Qwen3 step: add+norm reads the stream and writes the normed rows (the sum was made
     by the product before), the q/k kernel reads q|k|v, writes q and k back and k, v to the cache, SiLU*up reads 2I and writes I."""
@@ -426,7 +505,8 @@ def qwen3_kernel_bytes(cfg: dict, T: int) -> dict:
             "qk_norm_rope_kv_write": L * T * ((nh + 2 * kvh) + (nh + kvh) + 2 * kvh) * hd * 2}
 
 
-DESIGNS = {"tofilorn": (tofilorn_config, tofilorn_kernel_bytes), "kesozen": (kesozen_config, kesozen_kernel_bytes)}
+DESIGNS = {"tofilorn": (tofilorn_config, tofilorn_kernel_bytes), "kesozen": (kesozen_config, kesozen_kernel_bytes),
+           "rakizen": (rakizen_config, rakizen_kernel_bytes)}
 
 
 def float_issue_rate():
@@ -455,6 +535,8 @@ def design_run(design: str, widths, pk=None, layers: int = 16) -> dict:
                                 num_key_value_heads=8, intermediate_size=3 * width, vocab_size=32768, max_position_embeddings=8192)}
         if design == "kesozen":
             models["tofilorn"] = tofilorn_config(width, layers)       # its matrix-state scan is the delta rule's like kernel
+        if design == "rakizen":
+            models["kesozen"] = kesozen_config(width, layers)         # the float stream and the routed experts are its like kernels
         rec = {}
         for name, cfg in models.items():
             r = {}
@@ -495,7 +577,22 @@ def design_run(design: str, widths, pk=None, layers: int = 16) -> dict:
                     if rate:
                         r["prefill_2048"]["hgrn2_scan_frac_of_float_issue_rate"] = round(
                             work / (r["prefill_2048"]["own_kernels_ms"]["hgrn2_scan"] * 1e-3) / rate, 4)
-                if name == "kesozen":
+                if design == "rakizen":
+                    # attention over a prompt is arithmetic: the products of the keys a query sees against the measured
+                    # bfloat16 product of the library, whichever of the attention kernels ran
+                    own = r["prefill_2048"]["own_kernels_ms"]
+                    ms = sum(v for k, v in own.items() if "attention" in k)
+                    if ms:
+                        r["prefill_2048"]["attention_ms"] = round(ms, 4)
+                        r["prefill_2048"]["attention_frac_of_bf16_peak"] = round(
+                            attention_flops(cfg, PROMPT_LEN) / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+                    ms = sum(v for k, v in r["decode_batch8"]["own_kernels_ms"].items() if "attention" in k)
+                    if ms:
+                        # a decode step reads the keys and values its queries see, once
+                        by = attention_decode_bytes(cfg, 8, PROMPT_LEN)
+                        r["decode_batch8"]["attention_ms"] = round(ms, 4)
+                        r["decode_batch8"]["attention_frac_of_copy"] = round(by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                if name in ("kesozen", "rakizen"):
                     own = r["prefill_2048"]["own_kernels_ms"]
                     if own.get("delta_scan"):
                         # the delta rule is arithmetic too: a multiply and three multiply-adds per state element and token
@@ -615,7 +712,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(DESIGNS), default=None,
                     help="another workload instead of the default run")
-    ap.add_argument("--sizes", default="2048,4096", help="--workload tofilorn | kesozen: the widths to measure")
+    ap.add_argument("--sizes", default="2048,4096", help="--workload tofilorn | kesozen | rakizen: the widths to measure")
     ap.add_argument("--only", choices=["decode", "prefill", "attention"], default=None,
                     help="run one phase and print its time only (for short profiler captures)")
     args = ap.parse_args()
