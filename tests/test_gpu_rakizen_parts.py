@@ -102,6 +102,12 @@ CASES = {
     # equal sizes that the tensor-core kernels take, nothing rotated, a window of one key
     "window of one": ("attention_2", 64, dict(heads=2, kv_heads=2, dim=64, vdim=64, scale=0.3, softcap=5.0, mask={"size": 1},
                                               rot={"dims": 0, "base": 1.0})),
+    # equal head sizes of 64 and 128: in bfloat16 the tensor-core kernels run these (two key maps over one value head, blocks
+    # that end inside a page and inside a 64-key tile; a window longer than two tiles)
+    "two maps, 64 wide": ("attention", 64, dict(heads=4, kv_heads=2, dim=64, vdim=64, diff=0.3, scale=0.2, softcap=12.0, mask={"size": 50})),
+    "two maps, 128 wide": ("attention", 48, dict(heads=3, kv_heads=1, dim=128, vdim=128, diff=0.6, scale=0.15, softcap=25.0, mask={"size": 72})),
+    "window, 128 wide": ("attention_2", 64, dict(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.12, softcap=9.0, mask={"size": 141},
+                                                 rot={"dims": 64, "base": 1e4})),
     "window, 64 wide": ("attention_2", 64, dict(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.4, softcap=20.0, mask={"size": 70},
                                                 rot={"dims": 32, "base": 1e6})),
 }

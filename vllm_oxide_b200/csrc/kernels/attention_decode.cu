@@ -35,7 +35,7 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
   if (t_next - t != 1) return;                         // not a decoding request
   const int G = nh / kvh;
   const int pos = context - 1;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_key(pos, window, ep);
   // the key range in tiles of 64 from lo rounded down to a multiple of 16 (the copies work in runs of 16
   // keys); split s takes tiles [s*n/S, (s+1)*n/S): within one tile of each other
   const int lo16 = lo & ~15;
@@ -72,7 +72,7 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
     if (s < n_tiles) {
       tile_pages<DEC_TILE>(pages, table, block_size, start + s * DEC_TILE, lo, end);
       load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + s * DEC_STAGE_BYTES, kcache, vcache, pages, block_size, kvh, kh,
-                                             start + s * DEC_TILE, lo, end, num_pages, err);
+                                             start + s * DEC_TILE, lo, end, num_pages, err, value_heads(kvh, ep), value_head(kh, ep));
     }
     cp_async_commit();
   }
@@ -81,7 +81,7 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
     const int nxt = it + DEC_STAGES - 1;
     if (nxt < n_tiles) {
       load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + (nxt % DEC_STAGES) * DEC_STAGE_BYTES, kcache, vcache, pages, block_size,
-                                             kvh, kh, start + nxt * DEC_TILE, lo, end, num_pages, err);
+                                             kvh, kh, start + nxt * DEC_TILE, lo, end, num_pages, err, value_heads(kvh, ep), value_head(kh, ep));
       // the pages of the tile after that: looked up now, used in the next round
       if (nxt + 1 < n_tiles) tile_pages<DEC_TILE>(pages, table, block_size, start + (nxt + 1) * DEC_TILE, lo, end);
     }
@@ -97,10 +97,10 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
       for (int i = 0; i < 2; ++i) {
         const int key = k0 + i * 8 + tq * 2;
         const bool ok0 = key >= lo && key < end, ok1 = key + 1 >= lo && key + 1 < end;
-        s[i][0] = ok0 ? s[i][0] * sc : -INFINITY;
-        s[i][1] = ok1 ? s[i][1] * sc : -INFINITY;
-        s[i][2] = ok0 ? s[i][2] * sc : -INFINITY;
-        s[i][3] = ok1 ? s[i][3] * sc : -INFINITY;
+        s[i][0] = ok0 ? score2(s[i][0], sc, ep) : -INFINITY;
+        s[i][1] = ok1 ? score2(s[i][1], sc, ep) : -INFINITY;
+        s[i][2] = ok0 ? score2(s[i][2], sc, ep) : -INFINITY;
+        s[i][3] = ok1 ? score2(s[i][3], sc, ep) : -INFINITY;
       }
       softmax_pv_16keys(st, s, stage + DEC_TILE * ROW_BYTES + warp * 16 * ROW_BYTES, lane);
     }
@@ -145,7 +145,7 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
     const int head = kh * G + r;
     if (num_splits == 1) {
       const float Ls = L + sink_weight(ep, M);
-      out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(Ls > 0.f ? O / Ls * head_gate(ep, t, head) : 0.f);
+      store_out(out, (size_t)t * nh * HD + (size_t)head * HD + d, Ls > 0.f ? O / Ls * head_gate(ep, t, head) : 0.f, ep);
     } else {
       const size_t p = ((size_t)b * nh + head) * num_splits + split;
       part_o[p * HD + d] = val;
@@ -208,7 +208,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   if (t_next - t != 1) { pdl_wait(); return; }         // not a decoding request (uniform for the block)
   const int G = nh / kvh;
   const int pos = context - 1;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_key(pos, window, ep);
   const int lo16 = lo & ~(box_keys - 1);               // tiles start on a box boundary
   const int all_tiles = (pos + 1 - lo16 + DEC_TILE - 1) / DEC_TILE;
   const int tile_begin = (int)((long)split * all_tiles / num_splits);
@@ -245,8 +245,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
               const bool page_ok = page >= 0 && page < num_pages;
               if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
               const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+                const int vrow = page_ok ? (page * value_heads(kvh, ep) + value_head(kh, ep)) * block_size + tile_start % block_size : 0;
               tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
-              tma_load_3d(kt + DT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
+              tma_load_3d(kt + DT_TILE_BYTES, &tmV, 0, vrow, 0, &full[s]);
             } else {
 #pragma unroll
               for (int run = 0; run < 4; ++run) {
@@ -255,11 +256,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                 // a run nobody will read is filled from row 0 of the plane: finite values that the mask zeroes
                 const int key0 = tile_start + run * RUN_KEYS;
                 const int row = page_ok ? (pg[run] * kvh + kh) * block_size + key0 % block_size : 0;
+                const int vrow = page_ok ? (pg[run] * value_heads(kvh, ep) + value_head(kh, ep)) * block_size + key0 % block_size : 0;
                 // a 16-row box writes its slices 16 rows apart, the tile keeps them DEC_TILE rows apart: a copy per slice
 #pragma unroll
                 for (int c = 0; c < DT_SLICES; ++c) {
                   tma_load_3d(kt + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
-                  tma_load_3d(kt + DT_TILE_BYTES + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+                  tma_load_3d(kt + DT_TILE_BYTES + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, vrow, c, &full[s]);
                 }
               }
             }
@@ -309,10 +311,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         for (int i = 0; i < 2; ++i) {
           const int key = k0 + i * 8 + tq * 2;
           const bool ok0 = key >= lo && key < end, ok1 = key + 1 >= lo && key + 1 < end;
-          sv[i][0] = ok0 ? sv[i][0] * sc : -INFINITY;
-          sv[i][1] = ok1 ? sv[i][1] * sc : -INFINITY;
-          sv[i][2] = ok0 ? sv[i][2] * sc : -INFINITY;
-          sv[i][3] = ok1 ? sv[i][3] * sc : -INFINITY;
+          sv[i][0] = ok0 ? score2(sv[i][0], sc, ep) : -INFINITY;
+          sv[i][1] = ok1 ? score2(sv[i][1], sc, ep) : -INFINITY;
+          sv[i][2] = ok0 ? score2(sv[i][2], sc, ep) : -INFINITY;
+          sv[i][3] = ok1 ? score2(sv[i][3], sc, ep) : -INFINITY;
         }
         softmax_pv_16keys_swizzled<DEC_TILE>(st, sv, kt + DT_TILE_BYTES, warp * 16, lane);
       }
@@ -368,7 +370,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     const int head = kh * G + r;
     if (num_splits == 1) {
       const float Ls = L + sink_weight(ep, M);
-      out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(Ls > 0.f ? O / Ls * head_gate(ep, t, head) : 0.f);
+      store_out(out, (size_t)t * nh * HD + (size_t)head * HD + d, Ls > 0.f ? O / Ls * head_gate(ep, t, head) : 0.f, ep);
     } else if (cluster) {
       fo[idx] = val;
       if (d == 0) fl[r] = lse;
@@ -415,8 +417,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         O += w * v[sp];
       }
       W += sink_weight(ep, M);                // the sink counts once, whatever the number of splits
-      out[(size_t)t * nh * HD + (size_t)(kh * G) * HD + idx] =
-          __float2bfloat16_rn(W > 0.f ? O / W * head_gate(ep, t, kh * G + r) : 0.f);
+      store_out(out, (size_t)t * nh * HD + (size_t)(kh * G) * HD + idx, W > 0.f ? O / W * head_gate(ep, t, kh * G + r) : 0.f, ep);
     }
   }
   // nobody may leave while another block still reads its shared memory
@@ -493,7 +494,7 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
       const int t = cu_q[b];
       if (cu_q[b + 1] - t == 1) {                     // a decoding request (the others are the prefill kernel's)
         const int pos = context_lens[b] - 1;
-        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int lo = first_key(pos, window, ep);
         const int start = lo & ~(box_keys - 1);
         const int end = pos + 1;
         const int n_tiles = (end - start + DEC_TILE - 1) / DEC_TILE;
@@ -523,8 +524,9 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
                 const bool page_ok = page >= 0 && page < num_pages;
                 if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
                 const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+                const int vrow = page_ok ? (page * value_heads(kvh, ep) + value_head(kh, ep)) * block_size + tile_start % block_size : 0;
                 tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
-                tma_load_3d(kt + DT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
+                tma_load_3d(kt + DT_TILE_BYTES, &tmV, 0, vrow, 0, &full[s]);
               } else {
 #pragma unroll
                 for (int run = 0; run < 4; ++run) {
@@ -532,10 +534,11 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
                   if (!page_ok && pg[run] != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
                   const int key0 = tile_start + run * RUN_KEYS;
                   const int row = page_ok ? (pg[run] * kvh + kh) * block_size + key0 % block_size : 0;
+                const int vrow = page_ok ? (pg[run] * value_heads(kvh, ep) + value_head(kh, ep)) * block_size + key0 % block_size : 0;
 #pragma unroll
                   for (int c = 0; c < DT_SLICES; ++c) {
                     tma_load_3d(kt + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
-                    tma_load_3d(kt + DT_TILE_BYTES + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+                    tma_load_3d(kt + DT_TILE_BYTES + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, vrow, c, &full[s]);
                   }
                 }
               }
@@ -587,7 +590,7 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
       const int4 entry = ok ? queue[pair % DI_QUEUE] : make_int4(-1, 0, 0, 0);
       const bool more = entry.x >= 0;
       const int kh = more ? entry.x % kvh : 0, t = entry.y, pos = entry.z;
-      const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+      const int lo = first_key(pos, window, ep);
       const int start = lo & ~(box_keys - 1);
       const int end = pos + 1;
       const int n_tiles = more ? (end - start + DEC_TILE - 1) / DEC_TILE : 0;
@@ -621,10 +624,10 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
             for (int i = 0; i < 2; ++i) {
               const int key = k0 + i * 8 + tq * 2;
               const bool ok0 = key >= lo && key < end, ok1 = key + 1 >= lo && key + 1 < end;
-              sv[i][0] = ok0 ? sv[i][0] * sc : -INFINITY;
-              sv[i][1] = ok1 ? sv[i][1] * sc : -INFINITY;
-              sv[i][2] = ok0 ? sv[i][2] * sc : -INFINITY;
-              sv[i][3] = ok1 ? sv[i][3] * sc : -INFINITY;
+              sv[i][0] = ok0 ? score2(sv[i][0], sc, ep) : -INFINITY;
+              sv[i][1] = ok1 ? score2(sv[i][1], sc, ep) : -INFINITY;
+              sv[i][2] = ok0 ? score2(sv[i][2], sc, ep) : -INFINITY;
+              sv[i][3] = ok1 ? score2(sv[i][3], sc, ep) : -INFINITY;
             }
             softmax_pv_16keys_swizzled<DEC_TILE>(st, sv, kt + DT_TILE_BYTES, warp * 16, lane);
           }
@@ -669,8 +672,7 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
             O += wo[((size_t)w * G + r) * HD + d] * f;
           }
           L += sink_weight(ep, M);
-          out[(size_t)t * nh * HD + (size_t)(kh * G + r) * HD + d] =
-              __float2bfloat16_rn(L > 0.f ? O / L * head_gate(ep, t, kh * G + r) : 0.f);
+          store_out(out, (size_t)t * nh * HD + (size_t)(kh * G + r) * HD + d, L > 0.f ? O / L * head_gate(ep, t, kh * G + r) : 0.f, ep);
         }
       }
       asm volatile("bar.sync 1, %0;\n" ::"n"(DEC_WARPS * 32) : "memory");   // the buffer is free for the next pair
@@ -711,7 +713,7 @@ __global__ void attention_decode_combine_kernel(const float* part_o, const float
       O += w * part_o[(base + s) * HD + d];
     }
     W += sink_weight(ep, M);
-    out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W * head_gate(ep, t, head) : 0.f);
+    store_out(out, (size_t)t * nh * HD + (size_t)head * HD + d, W > 0.f ? O / W * head_gate(ep, t, head) : 0.f, ep);
   }
 }
 
@@ -738,7 +740,7 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
                                    const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
                                    int block_size, int window, float scale, long num_pages, int num_splits, float* scratch,
                                    unsigned* pairs_counter, int* err, cudaStream_t stream,
-                                   HeadEpilogue ep = HeadEpilogue{0, nullptr, 0}) {
+                                   HeadEpilogue ep = head_options(0, nullptr, 0, 0.f, 1.f, 0, 1)) {
   if (num_requests <= 0) return 0;
   if (kvh <= 0 || nh % kvh || nh / kvh > 16 || block_size <= 0 || num_splits < 1 || num_splits > 65535) return VOB_UNSUPPORTED;
   static bool configured = false;
@@ -842,16 +844,20 @@ VOB_API int vob_attention_decode_tma(const void* map_k, const void* map_v, const
 }
 
 // Both of the above (null maps: cp.async) with what may follow the softmax: `sink` (a silent extra entry of score 0) and
-// `gate` (bfloat16; head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]); null: none).
+// `gate` (bfloat16; head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]); null: none); and with other
+// rules for the scores: `softcap` > 0 (a score becomes softcap * tanh(score / softcap)), `chunk` > 0 (a query sees the
+// keys of its own block of `chunk` positions; `window` is then not looked at), `value_div` > 1 (the value plane has
+// kvh / value_div heads and key head k reads value head k / value_div), `out_float` (out is float).
 VOB_API int vob_attention_decode_ex(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
                                     const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                     const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
                                     int block_size, int window, float scale, long num_pages, int num_splits,
                                     float* scratch, unsigned* pairs_counter, int sink, const void* gate, long gate_stride,
-                                    int* err, cudaStream_t stream) {
+                                    float softcap, int chunk, int value_div, int out_float, int* err, cudaStream_t stream) {
+  if (value_div > 1 && kvh % value_div) return VOB_BAD_ARGUMENT;
   return attention_decode_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
                                  context_lens, num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
-                                 scratch, pairs_counter, err, stream, HeadEpilogue{sink, (const __nv_bfloat16*)gate, gate_stride});
+                                 scratch, pairs_counter, err, stream, head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float));
 }
 
 VOB_API int vob_attention_decode_has_tma() { return VOB_HD % 64 == 0 ? 1 : 0; }

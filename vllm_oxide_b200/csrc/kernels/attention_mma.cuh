@@ -53,14 +53,57 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// What may come after the softmax of a head.  `sink`: the softmax has a silent extra entry of score 0 that has no value; it
-// adds 2^(0 - M) to a denominator that is taken relative to M (scores in the base-2 domain).  `gate`: head h of token t is
-// multiplied by sigmoid(gate[t * gate_stride + h]).  {0, nullptr, 0} leaves the softmax as it is.
+// What a head's softmax does besides scaling and the causal mask, and what may come after it.  `sink`: the softmax has a
+// silent extra entry of score 0 that has no value; it adds 2^(0 - M) to a denominator that is taken relative to M (scores in
+// the base-2 domain).  `gate`: head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]).  `cap_out` > 0: a
+// score becomes cap * tanh(score / cap); the two factors are cap_in = scale / cap * 2 log2(e) (on the raw product) and
+// cap_out = cap * log2(e) (see head_options).  `chunk` > 0: a query sees only the keys of its own block of `chunk`
+// positions, counted from position 0.  `value_div` > 1: the value plane has kv_heads / value_div heads, and key head k
+// reads value head k / value_div (key heads that are several maps over one value head).  `out_float`: the output is float
+// (same shape), for heads that are combined before anything rounds them.  All zero leaves the softmax as it is.
 struct HeadEpilogue {
   int sink;
   const __nv_bfloat16* gate;
   long gate_stride;
+  float cap_in, cap_out;
+  int chunk;
+  int value_div;
+  int out_float;
 };
+__host__ inline HeadEpilogue head_options(int sink, const void* gate, long gate_stride, float softcap, float scale, int chunk,
+                                          int value_div, int out_float = 0) {
+  HeadEpilogue ep{sink, (const __nv_bfloat16*)gate, gate_stride, 0.f, 0.f, chunk > 0 ? chunk : 0, value_div > 1 ? value_div : 1,
+                  out_float};
+  if (softcap > 0.f) {
+    ep.cap_in = scale / softcap * 2.f * 1.4426950408889634f;
+    ep.cap_out = softcap * 1.4426950408889634f;
+  }
+  return ep;
+}
+// The first key that the query at `pos` sees.  It does not fall as `pos` grows.
+__device__ __forceinline__ int first_key(int pos, int window, const HeadEpilogue& ep) {
+  if (ep.chunk > 0) return pos / ep.chunk * ep.chunk;
+  return window > 0 ? max(0, pos - window + 1) : 0;
+}
+// A raw product as a score in the base-2 domain: raw * sc (sc = scale * log2(e)), capped if the head caps its scores:
+// cap * tanh(x) * log2(e) with tanh(x) = 1 - 2 / (1 + e^(2x)), which the hardware's 2^x and division give to a few ulp of 1
+// (the tanh approximation of the hardware is good to 2^-11 only, which a cap of 30 would turn into 1% of a weight).
+__device__ __forceinline__ float score2(float raw, float sc, const HeadEpilogue& ep) {
+  if (ep.cap_out > 0.f) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(raw * ep.cap_in));
+    return fmaf(-2.f * ep.cap_out, __fdividef(1.f, 1.f + e), ep.cap_out);
+  }
+  return raw * sc;
+}
+// Element i of the output.
+__device__ __forceinline__ void store_out(__nv_bfloat16* out, size_t i, float v, const HeadEpilogue& ep) {
+  if (ep.out_float) reinterpret_cast<float*>(out)[i] = v;
+  else out[i] = __float2bfloat16_rn(v);
+}
+// The value plane's heads and the value head of key head `kh`.
+__device__ __forceinline__ int value_heads(int kvh, const HeadEpilogue& ep) { return ep.value_div > 1 ? kvh / ep.value_div : kvh; }
+__device__ __forceinline__ int value_head(int kh, const HeadEpilogue& ep) { return ep.value_div > 1 ? kh / ep.value_div : kh; }
 // The sink's share of a denominator relative to M.  A maximum far below zero gives +inf, and the head's output 0: the limit.
 __device__ __forceinline__ float sink_weight(const HeadEpilogue& ep, float M) { return ep.sink ? exp2f(-M) : 0.f; }
 __device__ __forceinline__ float head_gate(const HeadEpilogue& ep, int t, int head) {
@@ -180,7 +223,7 @@ template <int TILE, int THREADS>
 __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* kcache,
                                              const __nv_bfloat16* vcache, const int (&pages)[TILE / RUN_KEYS],
                                              int block_size, int kvh, int kh, int tile_start, int begin, int end,
-                                             long num_pages, int* err) {
+                                             long num_pages, int* err, int v_kvh, int v_kh) {
   constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
   constexpr int RUN_CHUNKS = RUN_KEYS * CHUNKS;
   const long head_off = (long)kh * block_size * HD;
@@ -193,7 +236,7 @@ __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* k
     if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
     const long base = page_ok ? (long)page * page_elems + head_off + (long)(key0 % block_size) * HD : 0;
     const __nv_bfloat16* ksrc = kcache + base;
-    const __nv_bfloat16* vsrc = vcache + base;
+    const __nv_bfloat16* vsrc = vcache + (page_ok ? ((long)page * v_kvh + v_kh) * block_size * HD + (long)(key0 % block_size) * HD : 0);
     char* kdst = stage + run * RUN_KEYS * ROW_BYTES;
 #pragma unroll
     for (int c = threadIdx.x; c < RUN_CHUNKS; c += THREADS) {

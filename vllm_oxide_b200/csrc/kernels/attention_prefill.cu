@@ -70,11 +70,11 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
   // key range of the block and of this warp
   const int last_row = min(row0 + PF_ROWS, total_rows) - 1;
   const int blk_pos_lo = first_pos + row0 / G, blk_pos_hi = first_pos + last_row / G;
-  const int key_lo = window > 0 ? max(0, blk_pos_lo - window + 1) : 0;
+  const int key_lo = first_key(blk_pos_lo, window, ep);
   const int key_end = blk_pos_hi + 1;
   const int w_first = min(row0 + warp * 16, last_row), w_last = min(row0 + warp * 16 + 15, last_row);
   const int w_pos_lo = first_pos + w_first / G, w_pos_hi = first_pos + w_last / G;
-  const int w_key_lo = window > 0 ? max(0, w_pos_lo - window + 1) : 0;
+  const int w_key_lo = first_key(w_pos_lo, window, ep);
   const bool warp_active = row0 + warp * 16 < total_rows;
 
   WarpSoftmax st;
@@ -88,7 +88,7 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
     if (s < n_tiles) {
       tile_pages<PF_TILE>(pages, table, block_size, start + s * PF_TILE, key_lo, key_end);
       load_kv_tile<PF_TILE, PF_WARPS * 32>(smem + s * PF_STAGE_BYTES, kcache, vcache, pages, block_size, kvh, kh,
-                                           start + s * PF_TILE, key_lo, key_end, num_pages, err);
+                                           start + s * PF_TILE, key_lo, key_end, num_pages, err, value_heads(kvh, ep), value_head(kh, ep));
     }
     cp_async_commit();
   }
@@ -97,7 +97,7 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
     const int nxt = it + PF_STAGES - 1;
     if (nxt < n_tiles) {
       load_kv_tile<PF_TILE, PF_WARPS * 32>(smem + (nxt % PF_STAGES) * PF_STAGE_BYTES, kcache, vcache, pages, block_size, kvh,
-                                           kh, start + nxt * PF_TILE, key_lo, key_end, num_pages, err);
+                                           kh, start + nxt * PF_TILE, key_lo, key_end, num_pages, err, value_heads(kvh, ep), value_head(kh, ep));
       if (nxt + 1 < n_tiles) tile_pages<PF_TILE>(pages, table, block_size, start + (nxt + 1) * PF_TILE, key_lo, key_end);
     }
     cp_async_commit();
@@ -119,8 +119,8 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
             const int h = e >> 1;
             const int key = k0 + i * 8 + tq * 2 + (e & 1);
             bool ok = rvalid[h] && key <= rpos[h];
-            if (window > 0) ok = ok && key > rpos[h] - window;
-            s[i][e] = ok ? s[i][e] * sc : -INFINITY;
+            ok = ok && key >= first_key(rpos[h], window, ep);
+            s[i][e] = ok ? score2(s[i][e], sc, ep) : -INFINITY;
           }
         }
         softmax_pv_16keys(st, s, stage + PF_TILE * ROW_BYTES + sub * 16 * ROW_BYTES, lane);
@@ -140,6 +140,12 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
     const float lsum = st.l[h] + sink_weight(ep, st.m[h]);
     const float inv = lsum > 0.f ? head_gate(ep, t0 + rtok[h], rhead[h]) / lsum : 0.f;
     __nv_bfloat16* orow = out + (size_t)(t0 + rtok[h]) * nh * HD + (size_t)rhead[h] * HD + tq * 2;
+    if (ep.out_float) {
+      float* frow = reinterpret_cast<float*>(out) + (orow - out);
+#pragma unroll
+      for (int j = 0; j < DTILES; ++j) *reinterpret_cast<float2*>(frow + j * 8) = make_float2(st.o[j][2 * h] * inv, st.o[j][2 * h + 1] * inv);
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < DTILES; ++j)
       *reinterpret_cast<__nv_bfloat162*>(orow + j * 8) = __floats2bfloat162_rn(st.o[j][2 * h] * inv, st.o[j][2 * h + 1] * inv);
@@ -201,7 +207,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   const int* table = block_tables + (size_t)b * table_stride;
   const int last_row = min(row0 + PT_ROWS, total_rows) - 1;
   const int blk_pos_lo = first_pos + row0 / G, blk_pos_hi = first_pos + last_row / G;
-  const int key_lo = window > 0 ? max(0, blk_pos_lo - window + 1) : 0;
+  const int key_lo = first_key(blk_pos_lo, window, ep);
   const int key_end = blk_pos_hi + 1;
   const int start = key_lo / PT_TILE * PT_TILE;
   const int n_tiles = (key_end - start + PT_TILE - 1) / PT_TILE;
@@ -230,8 +236,9 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
               const bool page_ok = page >= 0 && page < num_pages;
               if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
               const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+                const int vrow = page_ok ? (page * value_heads(kvh, ep) + value_head(kh, ep)) * block_size + tile_start % block_size : 0;
               tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
-              tma_load_3d(kt + PT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
+              tma_load_3d(kt + PT_TILE_BYTES, &tmV, 0, vrow, 0, &full[s]);
             } else {
 #pragma unroll
               for (int run = 0; run < 4; ++run) {
@@ -240,11 +247,12 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
                 // a run nobody will read is filled from row 0 of the plane: finite values that the mask zeroes
                 const int key0 = tile_start + run * RUN_KEYS;
                 const int row = page_ok ? (pg[run] * kvh + kh) * block_size + key0 % block_size : 0;
+                const int vrow = page_ok ? (pg[run] * value_heads(kvh, ep) + value_head(kh, ep)) * block_size + key0 % block_size : 0;
                 // a 16-row box writes its slices 16 rows apart, the tile keeps them PT_TILE rows apart: a copy per slice
 #pragma unroll
                 for (int c = 0; c < PT_SLICES; ++c) {
                   tma_load_3d(kt + c * PT_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
-                  tma_load_3d(kt + PT_TILE_BYTES + c * PT_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+                  tma_load_3d(kt + PT_TILE_BYTES + c * PT_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, vrow, c, &full[s]);
                 }
               }
             }
@@ -291,7 +299,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   }
   const int w_first = min(row0 + warp * 16, last_row), w_last = min(row0 + warp * 16 + 15, last_row);
   const int w_pos_lo = first_pos + w_first / G, w_pos_hi = first_pos + w_last / G;
-  const int w_key_lo = window > 0 ? max(0, w_pos_lo - window + 1) : 0;
+  const int w_key_lo = first_key(w_pos_lo, window, ep);
   const bool warp_active = row0 + warp * 16 < total_rows;
   const bool all_rows = row0 + warp * 16 + 15 < total_rows;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -328,7 +336,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       }
       // mask only where the tile touches the diagonal, the window's edge, the range's ends or missing rows
       const bool need_mask = !all_rows || k0 + PT_TILE - 1 > w_pos_lo || k0 < key_lo ||
-                             (window > 0 && k0 < w_pos_hi - window + 1);
+                             k0 < first_key(w_pos_hi, window, ep);
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -337,8 +345,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
             const int h = e >> 1;
             const int key = k0 + i * 8 + tq * 2 + (e & 1);
             bool okk = rvalid[h] && key <= rpos[h] && key >= key_lo;
-            if (window > 0) okk = okk && key > rpos[h] - window;
-            sv[i][e] = okk ? sv[i][e] * sc : -INFINITY;
+            okk = okk && key >= first_key(rpos[h], window, ep);
+            sv[i][e] = okk ? score2(sv[i][e], sc, ep) : -INFINITY;
           }
       } else {
 #pragma unroll
@@ -408,6 +416,12 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     const float lsum = l[h] + sink_weight(ep, m[h]);
     const float inv = lsum > 0.f ? head_gate(ep, t0 + rtok[h], rhead[h]) / lsum : 0.f;
     __nv_bfloat16* orow = out + (size_t)(t0 + rtok[h]) * nh * HD + (size_t)rhead[h] * HD + tq * 2;
+    if (ep.out_float) {
+      float* frow = reinterpret_cast<float*>(out) + (orow - out);
+#pragma unroll
+      for (int j = 0; j < DTILES; ++j) *reinterpret_cast<float2*>(frow + j * 8) = make_float2(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < DTILES; ++j)
       *reinterpret_cast<__nv_bfloat162*>(orow + j * 8) = __floats2bfloat162_rn(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
@@ -423,7 +437,7 @@ static int attention_prefill_launch(const void* map_k, const void* map_v, const 
                                     const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                     const int* cu_q, const int* context_lens, int num_requests, int max_q, int nh, int kvh,
                                     int block_size, int window, float scale, long num_pages, int* err, cudaStream_t stream,
-                                    HeadEpilogue ep = HeadEpilogue{0, nullptr, 0}) {
+                                    HeadEpilogue ep = head_options(0, nullptr, 0, 0.f, 1.f, 0, 1)) {
   if (num_requests <= 0 || max_q <= 1) return 0;
   if (kvh <= 0 || nh % kvh || block_size <= 0 || kvh > 65535 || num_requests > 65535) return VOB_UNSUPPORTED;
   const long rows = (long)max_q * (nh / kvh);
@@ -477,13 +491,18 @@ VOB_API int vob_attention_prefill_tma(const void* map_k, const void* map_v, cons
 }
 
 // Both of the above (null maps: cp.async) with what may follow the softmax: `sink` (a silent extra entry of score 0) and
-// `gate` (bfloat16; head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]); null: none).
+// `gate` (bfloat16; head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]); null: none); and with other
+// rules for the scores: `softcap` > 0 (a score becomes softcap * tanh(score / softcap)), `chunk` > 0 (a query sees the
+// keys of its own block of `chunk` positions; `window` is then not looked at), `value_div` > 1 (the value plane has
+// kvh / value_div heads and key head k reads value head k / value_div), `out_float` (out is float).
 VOB_API int vob_attention_prefill_ex(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
                                      const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                      const int* cu_q, const int* context_lens, int num_requests, int max_q, int nh,
                                      int kvh, int block_size, int window, float scale, long num_pages, int sink,
-                                     const void* gate, long gate_stride, int* err, cudaStream_t stream) {
+                                     const void* gate, long gate_stride, float softcap, int chunk, int value_div, int out_float,
+                                     int* err, cudaStream_t stream) {
+  if (value_div > 1 && kvh % value_div) return VOB_BAD_ARGUMENT;
   return attention_prefill_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
                                   context_lens, num_requests, max_q, nh, kvh, block_size, window, scale, num_pages, err, stream,
-                                  HeadEpilogue{sink, (const __nv_bfloat16*)gate, gate_stride});
+                                  head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float));
 }

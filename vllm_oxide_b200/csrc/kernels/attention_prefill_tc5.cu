@@ -107,7 +107,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   const int first_pos = ctx - n;
   const int* table = block_tables + (size_t)b * table_stride;
   const int blk_pos_lo = first_pos + tok_base, blk_pos_hi = first_pos + min(tok_base + NQ * TT, n) - 1;
-  const int key_lo = window > 0 ? max(0, blk_pos_lo - window + 1) : 0;
+  const int key_lo = first_key(blk_pos_lo, window, ep);
   const int key_end = blk_pos_hi + 1;
   const int start = key_lo / F5_TILE * F5_TILE;
   const int n_tiles = (key_end - start + F5_TILE - 1) / F5_TILE;
@@ -118,7 +118,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     const int tok_first = tok_base + qt * TT;
     if (tok_first >= n) { jlo[qt] = jhi[qt] = 0; continue; }
     const int pos_lo = first_pos + tok_first, pos_hi = first_pos + min(tok_first + TT, n) - 1;
-    const int klo = window > 0 ? max(0, pos_lo - window + 1) : 0;
+    const int klo = first_key(pos_lo, window, ep);
     jlo[qt] = (klo - start) / F5_TILE;
     jhi[qt] = (pos_hi - start) / F5_TILE + 1;
   }
@@ -216,8 +216,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
             const bool page_ok = page >= 0 && page < num_pages;
             if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
             const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+            const int vrow = page_ok ? (page * value_heads(kvh, ep) + value_head(kh, ep)) * block_size + tile_start % block_size : 0;
             tma_load_3d(kt, &tmK, 0, row, 0, &kv_full[s]);
-            tma_load_3d(kt + F5_KV_BYTES, &tmV, 0, row, 0, &kv_full[s]);
+            tma_load_3d(kt + F5_KV_BYTES, &tmV, 0, vrow, 0, &kv_full[s]);
           } else {
 #pragma unroll
             for (int run = 0; run < 4; ++run) {
@@ -226,10 +227,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
               // a run nobody will read is filled from row 0 of the plane: finite values that the mask zeroes
               const int key0 = tile_start + run * RUN_KEYS;
               const int row = page_ok ? (pg[run] * kvh + kh) * block_size + key0 % block_size : 0;
+              const int vrow = page_ok ? (pg[run] * value_heads(kvh, ep) + value_head(kh, ep)) * block_size + key0 % block_size : 0;
 #pragma unroll
               for (int c = 0; c < F5_SLICES; ++c) {
                 tma_load_3d(kt + c * F5_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &kv_full[s]);
-                tma_load_3d(kt + F5_KV_BYTES + c * F5_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &kv_full[s]);
+                tma_load_3d(kt + F5_KV_BYTES + c * F5_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, vrow, c, &kv_full[s]);
               }
             }
           }
@@ -328,6 +330,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     const bool all_rows = tok_first + TT <= n;               // every token of the tile is the request's
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + qt * C::TILE_COLS;
     const float sc = scale * LOG2E;
+    const int row_lo = first_key(rpos, window, ep);
+    // a capped score, divided by the scale again: the steps below take maxima of raw products and scale them afterwards
+    const float uncap = ep.cap_out > 0.f ? 1.f / sc : 0.f;
     float m_ref = -INFINITY, l = 0.f;
     const int my_lo = jlo[qt], my_hi = jhi[qt];
     bool ok = true;
@@ -339,7 +344,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       t5_fence_after();
       const int k0 = start + j * F5_TILE;
       // mask only where the step touches the diagonal, the window's edge or missing rows
-      const bool need_mask = !all_rows || k0 + F5_TILE - 1 > t_pos_lo || (window > 0 && k0 < t_pos_hi - window + 1);
+      const bool need_mask = !all_rows || k0 + F5_TILE - 1 > t_pos_lo || k0 < first_key(t_pos_hi, window, ep);
       // (the rows past TR of a whole tile hold zeros: their scores are finite and go nowhere)
       float s[64];
       // the row's 64 scores of this step from tensor memory, masked
@@ -348,17 +353,18 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         t5_ld32_issue(lane_base + (i & 1) * F5_TILE, raw[0]);
         t5_ld32_issue(lane_base + (i & 1) * F5_TILE + 32, raw[1]);
         t5_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 64; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
+        if (ep.cap_out > 0.f) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) s[c] = score2(s[c], sc, ep) * uncap;
+        }
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 64; ++c) {
             const int key = k0 + c;
-            bool okk = valid && key <= rpos;
-            if (window > 0) okk = okk && key > rpos - window;
-            s[c] = okk ? __uint_as_float(raw[c >> 5][c & 31]) : -INFINITY;
+            s[c] = (valid && key <= rpos && key >= row_lo) ? s[c] : -INFINITY;
           }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 64; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
         }
       };
       // the maximum of the raw scores (the scale is positive): four chains of three-input maxima
@@ -485,7 +491,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
           t5_ld32_issue(lane_base + 2 * F5_TILE + c0, o[0]);
           t5_ld32_issue(lane_base + 2 * F5_TILE + c0 + 32, o[1]);
           t5_wait_ld();
-          if (valid) {
+          if (valid && ep.out_float) {
+            float* frow = reinterpret_cast<float*>(out) + (orow - out) + c0;
+#pragma unroll
+            for (int c = 0; c < 64; c += 4)
+              *reinterpret_cast<float4*>(frow + c) =
+                  make_float4(__uint_as_float(o[c >> 5][c & 31]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 1]) * inv,
+                              __uint_as_float(o[c >> 5][(c & 31) + 2]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 3]) * inv);
+          } else if (valid) {
 #pragma unroll
             for (int c = 0; c < 64; c += 16) {             // 32 bytes a store: whole sectors
               uint32_t v[8];
@@ -534,14 +547,16 @@ VOB_API int vob_attention_prefill_has_tc5() {
 // As vob_attention_prefill_tma (same tensor maps: 64-column slices, boxes of vob_attention_decode_box_keys rows), for
 // head sizes 64 and 128.  `query_tiles` is 1 or 2: how many tiles of 128 query rows a block takes.  `sink`: the softmax has a
 // silent extra entry of score 0; `gate` (bfloat16, may be null): head h of token t is multiplied by
-// sigmoid(gate[t * gate_stride + h]).
+// sigmoid(gate[t * gate_stride + h]).  `softcap`, `chunk`, `value_div`, `out_float`: as for vob_attention_prefill_ex.
 VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, const void* map_q, const void* map_o, const void* q, long q_stride, void* out,
                                       const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
                                       int num_requests, int max_q, int nh, int kvh, int block_size, int window, float scale,
                                       long num_pages, int query_tiles, int sink, const void* gate, long gate_stride,
-                                      int* err, cudaStream_t stream) {
+                                      float softcap, int chunk, int value_div, int out_float, int* err, cudaStream_t stream) {
 #if VOB_HD == 64 || VOB_HD == 128
-  const HeadEpilogue ep{sink, (const __nv_bfloat16*)gate, gate_stride};
+  const HeadEpilogue ep = head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float);
+  if (out_float && map_o) return VOB_BAD_ARGUMENT;           // whole tiles leave by the copy engine as bfloat16 only
+  if (value_div > 1 && kvh % value_div) return VOB_BAD_ARGUMENT;
   if (num_requests <= 0 || max_q <= 1) return 0;
   if (!map_k || !map_v) return VOB_BAD_ARGUMENT;
   if (((uintptr_t)out & 31) || ((uintptr_t)q & 15)) return VOB_BAD_ARGUMENT;     // 32-byte stores, 16-byte copies

@@ -618,11 +618,14 @@ def attention_decode_scratch_floats(head_dim: int, num_requests: int, nh: int, n
 
 def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, nh, kvh, hd,
                      window: int, scale: float, num_splits: int, scratch, err, use_tma: bool = True, pairs=None,
-                     sink: bool = False, gate=None, gate_stride: int = 0) -> None:
+                     sink: bool = False, gate=None, gate_stride: int = 0, softcap: float = 0.0, chunk: int = 0,
+                     value_div: int = 1) -> None:
     """Requests that bring exactly one token; the others are skipped.  `pairs`: two int32 zeros on the device that belong
     to this caller (`decode_pairs_counter`); with it, one split and more (request, kv head) pairs than blocks fit the GPU
     run as persistent blocks that draw their pairs from it (the kernel leaves it at zero), without it as one block per
-    pair.  Same bits either way.  `sink`, `gate`, `gate_stride`: as for paged_attention_generic."""
+    pair.  Same bits either way.  `sink`, `gate`, `gate_stride`, `softcap`, `chunk`: as for paged_attention_generic.
+    `value_div` > 1: `vcache` has kvh // value_div heads, and key head k reads value head k // value_div.  `out` is
+    bfloat16 or float32."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch, pairs, gate)
     assert pairs is None or (pairs.dtype == torch.int32 and pairs.numel() >= 2)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
@@ -637,7 +640,7 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
         map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
         block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window,
         ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(pairs if map_k is not None else None),
-        int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), _p(err), _stream()),
+        int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div), int(out.dtype == torch.float32), _p(err), _stream()),
         "attention_decode_tma" if map_k is not None else "attention_decode")
 
 
@@ -649,15 +652,18 @@ def decode_pairs_counter(device) -> torch.Tensor:
 
 def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, max_q, nh, kvh,
                       hd, window: int, scale: float, err, use_tma: bool = True, use_tc5: bool = True,
-                      query_tiles: int = 2, tiles_by_tma: bool = True, sink: bool = False, gate=None, gate_stride: int = 0) -> None:
+                      query_tiles: int = 2, tiles_by_tma: bool = True, sink: bool = False, gate=None, gate_stride: int = 0,
+                      softcap: float = 0.0, chunk: int = 0, value_div: int = 1) -> None:
     """Requests that bring more than one token; the others are skipped.  Head sizes 64 and 128 run on the tcgen05
     tensor cores (`use_tc5`; `tiles_by_tma` False makes that kernel bring its query tiles in by cp.async and store its
     output row by row also where TMA could), other multiples of 64 on mma.sync with TMA copies (`use_tma`), the rest with
-    cp.async.  `sink`, `gate`, `gate_stride`: as for paged_attention_generic."""
+    cp.async.  `sink`, `gate`, `gate_stride`, `softcap`, `chunk`: as for paged_attention_generic; `value_div`: as for
+    attention_decode."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, gate)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
     L = attention_lib(hd)
-    extras = (int(bool(sink)), _p(gate), ctypes.c_long(gate_stride))
+    extras = (int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div),
+              int(out.dtype == torch.float32))
     map_k = map_v = None
     if use_tma and L.vob_attention_decode_has_tma() and kcache.is_contiguous() and vcache.is_contiguous():
         bs = kcache.shape[2]
@@ -668,7 +674,7 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
             box_heads = L.vob_attention_prefill_q_box_heads(nh, kvh) if tiles_by_tma else 0
             map_q = tensor_map_heads(q, q_stride, nh, hd, box_heads, 128 // box_heads) if box_heads > 0 else None
             map_o = (tensor_map_heads(out, nh * hd, nh, hd, box_heads, 128 // box_heads)
-                     if box_heads > 0 and out.is_contiguous() and out.data_ptr() % 16 == 0 else None)
+                     if box_heads > 0 and out.is_contiguous() and out.data_ptr() % 16 == 0 and out.dtype == torch.bfloat16 else None)
             _check(L.vob_attention_prefill_tc5(
                 map_k, map_v, map_q, map_o, _p(q), ctypes.c_long(q_stride), _p(out), _p(block_tables), block_tables.shape[-1], _p(cu_q),
                 _p(context_lens), num_requests, max_q, nh, kvh, bs, window, ctypes.c_float(scale),

@@ -214,12 +214,19 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
     elements of each head of `out`.  `sink`: the softmax has a silent extra entry of score 0.  `gate`: a view whose element
     [t, h] (rows `gate_stride` apart) is head h's gate of token t; its output is multiplied by the sigmoid of it.
     `softcap` > 0: scores become softcap * tanh(score / softcap); `chunk` > 0: a query sees only keys of its own block of
-    `chunk` positions.  Values of another shape than the keys (their own head size, or fewer heads) and a float `out`
-    beside 16-bit inputs go to the plain kernel."""
+    `chunk` positions.  Values of another shape than the keys (their own head size, or fewer heads)
+    go to the plain kernel; values of the keys' head size in a whole fraction of the keys' heads (key
+    head k reads value head k / fraction) stay with the tensor-core kernels."""
     tables = ctx.block_tables[group]
     own_values = tuple(values.shape) != tuple(keys.shape)
+    # values of the keys' head size in fewer heads: key heads that are several maps over one value head
+    value_div = 1
+    if (own_values and values.shape[0] == keys.shape[0] and values.shape[2:] == keys.shape[2:] and values.shape[1] > 0
+            and keys.shape[1] % values.shape[1] == 0 and FAST_CAP_AND_CHUNK):
+        value_div, own_values = keys.shape[1] // values.shape[1], False
     fast = kernels.has_fast_attention(q.dtype, hd, nh // kvh) and scale > 0.0      # the tcgen05 kernel takes maxima before it scales
-    fast = fast and not own_values and out.dtype == q.dtype and (FAST_CAP_AND_CHUNK or not (softcap or chunk))
+    fast = fast and not own_values and (FAST_CAP_AND_CHUNK or not (softcap or chunk))
+    fast = fast and (out.dtype == q.dtype or (out.dtype == torch.float32 and FAST_CAP_AND_CHUNK))
     if not fast or ((sink or gate is not None) and not FAST_SINK_AND_GATE):
         kernels.paged_attention_generic(q, q_stride, out, keys, values, tables, ctx.token_req, ctx.positions, T,
                                         nh, kvh, hd, window, scale, ctx.err, value_dim=value_dim, sink=sink, gate=gate,
@@ -227,23 +234,24 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
         return values.shape[3] if own_values else (hd if value_dim is None else value_dim)
     B = ctx.launch_requests
     if ctx.num_decode > 0:
-        n_keys = ctx.max_context if window == 0 else min(ctx.max_context, window)
+        n_keys = min(ctx.max_context, chunk or window or ctx.max_context)
         splits = decode_splits(B, kvh, n_keys, kernels.sm_count())
         n = kernels.attention_decode_scratch_floats(hd, B, nh, splits)
         scratch = ctx.ws.get_flat("attention_decode_scratch", n, torch.float32) if n else None
         kernels.attention_decode(q, q_stride, out, keys, values, tables, ctx.cu_q, ctx.context_lens, B, nh,
                                  kvh, hd, window, scale, splits, scratch, ctx.err, pairs=pairs, sink=sink, gate=gate,
-                                 gate_stride=gate_stride)
+                                 gate_stride=gate_stride, softcap=softcap, chunk=chunk, value_div=value_div)
     if ctx.max_q > 1:
         kernels.attention_prefill(q, q_stride, out, keys, values, tables, ctx.cu_q, ctx.context_lens, B,
-                                  ctx.max_q, nh, kvh, hd, window, scale, ctx.err, sink=sink, gate=gate, gate_stride=gate_stride)
+                                  ctx.max_q, nh, kvh, hd, window, scale, ctx.err, sink=sink, gate=gate, gate_stride=gate_stride,
+                                  softcap=softcap, chunk=chunk, value_div=value_div)
     return hd
 
 
 # Whether the tensor-core attention kernels take a softmax with a sink and a gate on the heads (else the plain kernel does).
 FAST_SINK_AND_GATE = True
-# Whether they take capped scores and blocks of positions (else the plain kernel does).
-FAST_CAP_AND_CHUNK = False
+# Whether they take capped scores, blocks of positions and values with fewer heads than keys (else the plain kernel does).
+FAST_CAP_AND_CHUNK = True
 
 DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)
 
