@@ -603,7 +603,8 @@ def design_run(design: str, widths, pk=None, layers: int = 16) -> dict:
                             r["prefill_2048"]["delta_scan_frac_of_float_issue_rate"] = round(work / (own["delta_scan"] * 1e-3) / rate, 4)
                     if own.get("moe_gemm_tc5"):
                         # the experts' products against the measured bfloat16 product of the library
-                        flops = sum(4 * PROMPT_LEN * l["mlp"]["router"]["top"] * cfg["width"] * l["mlp"]["expert"]["ff"]
+                        # (two products an expert; three where it is gated)
+                        flops = sum((6 if name == "rakizen" else 4) * PROMPT_LEN * l["mlp"]["router"]["top"] * cfg["width"] * l["mlp"]["expert"]["ff"]
                                     for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
                         r["prefill_2048"]["moe_gemm_tc5_frac_of_bf16_peak"] = round(flops / (own["moe_gemm_tc5"] * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
             rec[name] = r

@@ -18,6 +18,7 @@
 namespace vob {
 
 constexpr int QP_NT = 256;
+constexpr int QP_MAX_ROT = 512;   // the most elements of a head that turn
 
 template <typename T>
 __global__ void __launch_bounds__(QP_NT)
@@ -26,6 +27,7 @@ rownorm_rope_kv_write_kernel(T* qkv, long row_stride, const int* __restrict__ po
                              T* kcache, T* vcache, int nh, int kvh, int kd, int vh, int vd, int rot_dim, int interleaved,
                              float eps, long num_slots, int block_size, int write_kv, int* err) {
   __shared__ float scratch[32];
+  __shared__ float2 turn[QP_MAX_ROT / 2];               // (cos, sin) of every angle
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int pos = positions[t];
@@ -42,20 +44,91 @@ rownorm_rope_kv_write_kernel(T* qkv, long row_stride, const int* __restrict__ po
   }
   T* row = qkv + (size_t)t * row_stride;
   const int nq = nh * kd, nk = kvh * kd, nv = vh * vd;
+  const int half = rot_dim >> 1;
+  // 16-bit rows whose heads and rotated parts are whole groups of 8 elements, with neighbours turning together, move by
+  // 16-byte accesses (same arithmetic)
+  const bool wide = sizeof(T) == 2 && kd % 8 == 0 && vd % 8 == 0 && rot_dim % 8 == 0 && (interleaved || rot_dim == 0) &&
+                    row_stride % 8 == 0 && ((uintptr_t)qkv & 15) == 0;
+  // the angles' sines and cosines, once a token (every head turns by the same ones)
+  for (int j = threadIdx.x; j < half; j += QP_NT) sincosf(__fmul_rn((float)pos, freq[j]), &turn[j].y, &turn[j].x);
   float inv_q = 1.f, inv_k = 1.f;
   if (wq) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < nq; i += QP_NT) { const float x = to_f<T>(row[i]); ss = fmaf(x, x, ss); }
-    inv_q = 1.f / sqrtf(block_sum<QP_NT>(ss, scratch) / (float)nq + eps);
-  }
-  if (wk) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < nk; i += QP_NT) { const float x = to_f<T>(row[nq + i]); ss = fmaf(x, x, ss); }
-    inv_k = 1.f / sqrtf(block_sum<QP_NT>(ss, scratch) / (float)nk + eps);
+    // the sums of squares of q and of k, each added up in the same order whatever else the step holds
+    float sq = 0.f, sk = 0.f;
+    if (wide) {
+      for (int i = threadIdx.x * 8; i < nq + nk; i += QP_NT * 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) { const float x = __bfloat162float(e[c]); ss = fmaf(x, x, ss); }
+        if (i < nq) sq += ss; else sk += ss;
+      }
+    } else {
+      for (int i = threadIdx.x; i < nq; i += QP_NT) { const float x = to_f<T>(row[i]); sq = fmaf(x, x, sq); }
+      for (int i = threadIdx.x; i < nk; i += QP_NT) { const float x = to_f<T>(row[nq + i]); sk = fmaf(x, x, sk); }
+    }
+    inv_q = 1.f / sqrtf(block_sum<QP_NT>(sq, scratch) / (float)nq + eps);
+    inv_k = 1.f / sqrtf(block_sum<QP_NT>(sk, scratch) / (float)nk + eps);
+  } else {
+    __syncthreads();                                    // the angles are there
   }
   const size_t page = put ? (size_t)(slot / block_size) : 0;
   const int in_page = put ? slot % block_size : 0;
-  const int half = rot_dim >> 1;
+  if (wide) {
+    if constexpr (sizeof(T) == 2) {
+      const int chunks = kd / 8;
+      for (int it = threadIdx.x; it < (nh + kvh) * chunks; it += QP_NT) {
+        const int head = it / chunks, a0 = it % chunks * 8;
+        const bool is_q = head < nh;
+        if (!is_q && !put) continue;
+        if (is_q && !wq && a0 >= rot_dim) continue;            // nothing changes it
+        const float inv = is_q ? inv_q : inv_k;
+        const float* w = is_q ? wq : wk;
+        const int hoff = is_q ? head * kd : (head - nh) * kd;
+        T* src = row + (is_q ? 0 : nq) + hoff;
+        T* dst = is_q ? src : kcache + ((page * kvh + (head - nh)) * block_size + in_page) * (size_t)kd;
+        auto normed = [&](int at, float (&x)[8]) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(src + at);
+          const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) x[c] = __bfloat162float(e[c]);
+          if (w) {
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(w + hoff + at));
+            const float4 g1 = __ldg(reinterpret_cast<const float4*>(w + hoff + at) + 1);
+            const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) x[c] = __fmul_rn(__fmul_rn(x[c], inv), g[c]);
+          }
+        };
+        float x[8], y[8];
+        normed(a0, x);
+        if (a0 < rot_dim) {
+#pragma unroll
+          for (int c = 0; c < 8; c += 2) {
+            const float2 cs = turn[(a0 + c) >> 1];
+            y[c] = __fsub_rn(__fmul_rn(x[c], cs.x), __fmul_rn(x[c + 1], cs.y));
+            y[c + 1] = __fadd_rn(__fmul_rn(x[c + 1], cs.x), __fmul_rn(x[c], cs.y));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) y[c] = x[c];
+        }
+        uint4 packed;
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) p2[c] = __floats2bfloat162_rn(y[2 * c], y[2 * c + 1]);
+        *reinterpret_cast<uint4*>(dst + a0) = packed;
+      }
+      if (put)
+        for (int i = threadIdx.x * 8; i < nv; i += QP_NT * 8) {
+          const int head = i / vd, d = i % vd;
+          *reinterpret_cast<uint4*>(vcache + ((page * vh + head) * block_size + in_page) * (size_t)vd + d) =
+              *reinterpret_cast<const uint4*>(row + nq + nk + i);
+        }
+    }
+    return;
+  }
   // q and k: a thread takes a pair of elements that turn together, or a single element behind the rotated part
   const int per_head = half + (kd - rot_dim);          // work items of a head
   const int items = (nh + kvh) * per_head;
@@ -72,8 +145,7 @@ rownorm_rope_kv_write_kernel(T* qkv, long row_stride, const int* __restrict__ po
       const int a = interleaved ? 2 * j : j, b = interleaved ? 2 * j + 1 : j + half;
       float u = to_f<T>(src[a]), v = to_f<T>(src[b]);
       if (w) { u = __fmul_rn(__fmul_rn(u, inv), w[hoff + a]); v = __fmul_rn(__fmul_rn(v, inv), w[hoff + b]); }
-      float sn, cs;
-      sincosf(__fmul_rn((float)pos, freq[j]), &sn, &cs);
+      const float cs = turn[j].x, sn = turn[j].y;
       dst[a] = from_f<T>(__fsub_rn(__fmul_rn(u, cs), __fmul_rn(v, sn)));
       dst[b] = from_f<T>(__fadd_rn(__fmul_rn(v, cs), __fmul_rn(u, sn)));
     } else {
@@ -126,7 +198,8 @@ VOB_API int vob_rownorm_rope_kv_write(void* qkv, long row_stride, const int* pos
                                       int block_size, int write_kv, int dtype, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (kd <= 0 || vd <= 0 || nh <= 0 || kvh <= 0 || vh <= 0 || block_size <= 0 || rot_dim < 0 || rot_dim > kd || rot_dim % 2 ||
-      (rot_dim > 0 && !freq) || (wq == nullptr) != (wk == nullptr))
+      (rot_dim > 0 && !freq) || (wq == nullptr) != (wk == nullptr) ||
+      rot_dim > QP_MAX_ROT)
     return VOB_BAD_ARGUMENT;
   if (dtype == VOB_F32)
     return launch_kernel(rownorm_rope_kv_write_kernel<float>, dim3(T), QP_NT, 0, stream, (float*)qkv, row_stride, positions,
