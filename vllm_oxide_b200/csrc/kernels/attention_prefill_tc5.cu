@@ -332,7 +332,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     const float sc = scale * LOG2E;
     const int row_lo = first_key(rpos, window, ep);
     // a capped score, divided by the scale again: the steps below take maxima of raw products and scale them afterwards
-    const float uncap = ep.cap_out > 0.f ? 1.f / sc : 0.f;
+    const float cap_raw = ep.cap_out > 0.f ? ep.cap_out / sc : 0.f, cap_raw2 = -2.f * cap_raw;
     float m_ref = -INFINITY, l = 0.f;
     const int my_lo = jlo[qt], my_hi = jhi[qt];
     bool ok = true;
@@ -357,7 +357,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         for (int c = 0; c < 64; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
         if (ep.cap_out > 0.f) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) s[c] = score2(s[c], sc, ep) * uncap;
+          for (int c = 0; c < 64; ++c) s[c] = fmaf(cap_raw2, __fdividef(1.f, 1.f + fast_exp2(s[c] * ep.cap_in)), cap_raw);
         }
         if (need_mask) {
 #pragma unroll
