@@ -66,6 +66,12 @@ CONFIGS = {
         "layers": [_moe(_windowed(1, 1, 40, 24, 1, 0, 100.0, 0.15, 25.0), 48, 5, 1, 5, 3, 0.7),
                    _dense(_two_map(1, 1, 36, 20, 2, 0.3, 0.25, 6.0), 64),
                    _moe(_windowed(6, 2, 16, 16, 90, 16, 777.0, 0.3, 40.0), 33, 6, 3, 3, 2, 2.0)]}),
+    # sizes that are no multiples of 8: width, vocabulary, head sizes, feed-forward and expert widths; the whole model is one
+    # loop that runs twice; pages of 16 under a window of 17 and blocks of 15
+    "D": dict(block_size=16, config={
+        "architecture": "Rakizen", "vocab": 211, "width": 100, "norm": {"eps": 1e-6}, "loop": {"start": 0, "stop": 2, "times": 2},
+        "layers": [_moe(_two_map(5, 5, 12, 28, 15, 0.35, 0.3, 9.0), 30, 9, 2, 3, 2, 1.2),
+                   _dense(_windowed(3, 3, 20, 12, 17, 10, 3000.0, 0.22, 14.0), 150)]}),
 }
 NAMES = sorted(CONFIGS)
 DTYPES = ["float32", "bfloat16"]

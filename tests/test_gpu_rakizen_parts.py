@@ -108,6 +108,11 @@ CASES = {
     "two maps, 128 wide": ("attention", 48, dict(heads=3, kv_heads=1, dim=128, vdim=128, diff=0.6, scale=0.15, softcap=25.0, mask={"size": 72})),
     "window, 128 wide": ("attention_2", 64, dict(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.12, softcap=9.0, mask={"size": 141},
                                                  rot={"dims": 64, "base": 1e4})),
+    # equal head sizes that the mma.sync kernels take in bfloat16: by cp.async (32, 96) and by TMA (192)
+    "two maps, 32 wide": ("attention", 40, dict(heads=2, kv_heads=1, dim=32, vdim=32, diff=0.2, scale=0.3, softcap=10.0, mask={"size": 21})),
+    "two maps, 192 wide": ("attention", 48, dict(heads=2, kv_heads=2, dim=192, vdim=192, diff=0.4, scale=0.1, softcap=18.0, mask={"size": 64})),
+    "window, 96 wide": ("attention_2", 56, dict(heads=4, kv_heads=2, dim=96, vdim=96, scale=0.14, softcap=7.0, mask={"size": 45},
+                                                rot={"dims": 48, "base": 2e4})),
     "window, 64 wide": ("attention_2", 64, dict(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.4, softcap=20.0, mask={"size": 70},
                                                 rot={"dims": 32, "base": 1e6})),
 }
