@@ -49,9 +49,14 @@ def test_the_plan_follows_the_configuration():
     assert names["l1.mix.q.norm"] == (96,) and names["l1.mix.k.norm"] == (32,) and names["l1.mix.v"] == (16, 48)
     assert names["l1.mlp.e5.gate"] == (20, 48) and names["l1.mlp.router"] == (6, 48) and "l1.mlp.correction" not in names
     assert names["l0.norm1.b"] == (48,) and names["final.norm.b"] == (48,) and "l2.mlp.gate" not in names
-    specs = model.cache_specs()
+    # the 32-bit model holds keys and values in their own sizes; the bfloat16 model pads both to one size that the
+    # tensor-core attention kernels take (the next multiple of 16 of the larger)
+    specs = CausalLM(plan, torch.float32, "cpu").cache_specs()
     assert (specs[0].kv_heads, specs[0].head_dim, specs[0].value_shape(), specs[0].chunk, specs[0].window) == (4, 24, (2, 40), 50, 0)
-    assert (specs[1].kv_heads, specs[1].value_shape(), specs[1].chunk, specs[1].window) == (1, (1, 16), 0, 37)
+    assert (specs[1].kv_heads, specs[1].head_dim, specs[1].value_shape(), specs[1].chunk, specs[1].window) == (1, 32, (1, 16), 0, 37)
+    specs = model.cache_specs()
+    assert (specs[0].kv_heads, specs[0].head_dim, specs[0].value_shape(), specs[0].chunk, specs[0].window) == (4, 48, (2, 48), 50, 0)
+    assert (specs[1].kv_heads, specs[1].head_dim, specs[1].value_shape(), specs[1].chunk, specs[1].window) == (1, 32, (1, 32), 0, 37)
     assert RakizenConfig.from_dict(cfg.to_dict()) == cfg
 
 

@@ -3,7 +3,9 @@
 //
 //   rownorm_rope_kv_write   A token's row holds nh query heads and kvh key heads of kd elements, then vh value heads of vd
 //                           elements (whatever follows is not touched).  With norm weights, q (all nh * kd elements at
-//                           once) and k (all kvh * kd) each pass an RMS norm with a gain: x / sqrt(mean(x^2) + eps) * w.
+//                           once) and k (all kvh * kd) each pass an RMS norm with a gain: x / sqrt(mean(x^2) + eps) * w
+//                           (the mean counts kd_norm elements a head: heads padded with zeros behind them count as
+//                           their own size).
 //                           Then the first rot_dim elements of every q and k head turn by the angle float(position) *
 //                           freq[i]: element 2i with 2i + 1 (`interleaved`) or i with i + rot_dim/2.  q is written back in
 //                           place; k goes to the key plane [pages, kvh, block_size, kd] and v, as projected, to the value
@@ -25,7 +27,7 @@ __global__ void __launch_bounds__(QP_NT)
 rownorm_rope_kv_write_kernel(T* qkv, long row_stride, const int* __restrict__ positions, const int* __restrict__ slots,
                              const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ freq,
                              T* kcache, T* vcache, int nh, int kvh, int kd, int vh, int vd, int rot_dim, int interleaved,
-                             float eps, long num_slots, int block_size, int write_kv, int* err) {
+                             float eps, long num_slots, int block_size, int write_kv, int* err, int kd_norm) {
   __shared__ float scratch[32];
   __shared__ float2 turn[QP_MAX_ROT / 2];               // (cos, sin) of every angle
   pdl_launch_dependents();
@@ -68,8 +70,8 @@ rownorm_rope_kv_write_kernel(T* qkv, long row_stride, const int* __restrict__ po
       for (int i = threadIdx.x; i < nq; i += QP_NT) { const float x = to_f<T>(row[i]); sq = fmaf(x, x, sq); }
       for (int i = threadIdx.x; i < nk; i += QP_NT) { const float x = to_f<T>(row[nq + i]); sk = fmaf(x, x, sk); }
     }
-    inv_q = 1.f / sqrtf(block_sum<QP_NT>(sq, scratch) / (float)nq + eps);
-    inv_k = 1.f / sqrtf(block_sum<QP_NT>(sk, scratch) / (float)nk + eps);
+    inv_q = 1.f / sqrtf(block_sum<QP_NT>(sq, scratch) / (float)(nh * kd_norm) + eps);
+    inv_k = 1.f / sqrtf(block_sum<QP_NT>(sk, scratch) / (float)(kvh * kd_norm) + eps);
   } else {
     __syncthreads();                                    // the angles are there
   }
@@ -166,7 +168,7 @@ rownorm_rope_kv_write_kernel(T* qkv, long row_stride, const int* __restrict__ po
 template <typename T, typename TA>
 __global__ void __launch_bounds__(128)
 diff_heads_combine_kernel(const TA* a, const T* gate, long gate_stride, T* out, int heads, int group, int vd, float lambda,
-                          float post, float eps) {
+                          float post, float eps, int vd_norm) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -180,7 +182,7 @@ diff_heads_combine_kernel(const TA* a, const T* gate, long gate_stride, T* out, 
     const float o = __fsub_rn(to_f<TA>(a1[d]), __fmul_rn(lambda, to_f<TA>(a2[d])));
     ss = fmaf(o, o, ss);
   }
-  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)vd + eps);
+  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)vd_norm + eps);
   for (int d = lane; d < vd; d += 32) {
     float o = __fsub_rn(to_f<TA>(a1[d]), __fmul_rn(lambda, to_f<TA>(a2[d]))) * inv * post;
     if (gate) o *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * gate_stride + (size_t)h * vd + d])));
@@ -195,7 +197,8 @@ using namespace vob;
 VOB_API int vob_rownorm_rope_kv_write(void* qkv, long row_stride, const int* positions, const int* slots, const float* wq,
                                       const float* wk, const float* freq, void* kcache, void* vcache, int T, int nh, int kvh,
                                       int kd, int vh, int vd, int rot_dim, int interleaved, float eps, long num_slots,
-                                      int block_size, int write_kv, int dtype, int* err, cudaStream_t stream) {
+                                      int block_size, int write_kv, int dtype, int kd_norm, int* err, cudaStream_t stream) {
+  if (kd_norm <= 0 || kd_norm > kd) return VOB_BAD_ARGUMENT;
   if (T <= 0) return 0;
   if (kd <= 0 || vd <= 0 || nh <= 0 || kvh <= 0 || vh <= 0 || block_size <= 0 || rot_dim < 0 || rot_dim > kd || rot_dim % 2 ||
       (rot_dim > 0 && !freq) || (wq == nullptr) != (wk == nullptr) ||
@@ -204,23 +207,25 @@ VOB_API int vob_rownorm_rope_kv_write(void* qkv, long row_stride, const int* pos
   if (dtype == VOB_F32)
     return launch_kernel(rownorm_rope_kv_write_kernel<float>, dim3(T), QP_NT, 0, stream, (float*)qkv, row_stride, positions,
                          slots, wq, wk, freq, (float*)kcache, (float*)vcache, nh, kvh, kd, vh, vd, rot_dim, interleaved, eps,
-                         num_slots, block_size, write_kv, err);
+                         num_slots, block_size, write_kv, err, kd_norm);
   if (dtype == VOB_BF16)
     return launch_kernel(rownorm_rope_kv_write_kernel<__nv_bfloat16>, dim3(T), QP_NT, 0, stream, (__nv_bfloat16*)qkv,
                          row_stride, positions, slots, wq, wk, freq, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, kvh,
-                         kd, vh, vd, rot_dim, interleaved, eps, num_slots, block_size, write_kv, err);
+                         kd, vh, vd, rot_dim, interleaved, eps, num_slots, block_size, write_kv, err, kd_norm);
   return VOB_BAD_ARGUMENT;
 }
 
-// a: float (`a_float`) or `dtype`; gate (null: none) and out of `dtype`.
+// a: float (`a_float`) or `dtype`; gate (null: none) and out of `dtype`.  The mean counts vd_norm elements of a head (heads
+// padded with zeros count as their own size).
 VOB_API int vob_diff_heads_combine(const void* a, int a_float, const void* gate, long gate_stride, void* out, int T, int heads,
-                                   int group, int vd, float lambda, float post, float eps, int dtype, cudaStream_t stream) {
+                                   int group, int vd, float lambda, float post, float eps, int dtype, int vd_norm,
+                                   cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (heads <= 0 || group <= 0 || heads % group || vd <= 0) return VOB_BAD_ARGUMENT;
+  if (heads <= 0 || group <= 0 || heads % group || vd <= 0 || vd_norm <= 0 || vd_norm > vd) return VOB_BAD_ARGUMENT;
   dim3 grid(T, (heads + 3) / 4);
 #define VOB_DC(TYPE, TA)                                                                                              \
   return launch_kernel(diff_heads_combine_kernel<TYPE, TA>, grid, 128, 0, stream, (const TA*)a, (const TYPE*)gate,    \
-                       gate_stride, (TYPE*)out, heads, group, vd, lambda, post, eps)
+                       gate_stride, (TYPE*)out, heads, group, vd, lambda, post, eps, vd_norm)
   if (dtype == VOB_F32) { VOB_DC(float, float); }
   if (dtype == VOB_BF16) {
     if (a_float) { VOB_DC(__nv_bfloat16, float); }

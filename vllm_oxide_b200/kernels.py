@@ -234,11 +234,12 @@ def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, toke
 
 
 def rownorm_rope_kv_write(qkv, positions, slots, wq, wk, rule, kcache, vcache, num_tokens: int, nh: int, kvh: int, kd: int,
-                          eps: float, write_kv: bool, err) -> None:
+                          eps: float, write_kv: bool, err, kd_norm: Optional[int] = None) -> None:
     """A merged q|k|v row whose keys and values have shapes of their own: q (all heads at once) and k each pass an RMS norm
     with a gain (wq, wk float, both or neither), the front of every q and k head turns by computed angles (`rule` with
     `frequencies`; rotary_dim 0 turns nothing), q is written back in place, k goes to `kcache` [pages, kvh, page size, kd]
-    and v as projected to `vcache` [pages, value heads, page size, value size]."""
+    and v as projected to `vcache` [pages, value heads, page size, value size].  `kd_norm`: how many elements of a head
+    count in the norms' means (heads that are padded with zeros behind their own elements; default kd)."""
     _cuda(qkv, positions, slots, wq, wk, rule.frequencies, kcache, vcache)
     if rule.rotary_dim > 0 and (rule.frequencies is None or rule.amplitude != 1.0):
         raise KernelError("rownorm_rope_kv_write turns by computed angles: the rule needs `frequencies` and amplitude 1")
@@ -250,22 +251,24 @@ def rownorm_rope_kv_write(qkv, positions, slots, wq, wk, rule, kcache, vcache, n
                                            _p(rule.frequencies), _p(kcache), _p(vcache), num_tokens, nh, kvh, kd,
                                            vcache.shape[1], vcache.shape[3], rule.rotary_dim, int(rule.interleaved),
                                            ctypes.c_float(eps), ctypes.c_long(kcache.shape[0] * kcache.shape[2]),
-                                           kcache.shape[2], int(write_kv), _code(qkv.dtype), _p(err), _stream()),
+                                           kcache.shape[2], int(write_kv), _code(qkv.dtype), int(kd_norm or kd), _p(err),
+                                           _stream()),
            "rownorm_rope_kv_write")
 
 
 def diff_heads_combine(a, gate, gate_stride: int, out, num_tokens: int, heads: int, group: int, vd: int, lam: float, post: float,
-                       eps: float) -> None:
+                       eps: float, vd_norm: Optional[int] = None) -> None:
     """out[t, h] = (a1 - lam * a2) / sqrt(mean((a1 - lam * a2)^2) + eps) * post * sigmoid(gate[t, h]) for heads that are
     two maps: `a` [tokens, 2 * heads * vd] (float32, or out's type) holds, per key/value head, the first maps of its
     `group` heads and then their second maps; `gate` (None: none): a view with rows `gate_stride` apart, heads * vd numbers
-    a token; `out` [tokens, heads * vd] in the heads' own order."""
+    a token; `out` [tokens, heads * vd] in the heads' own order.  `vd_norm`: how many elements of a head count in the mean
+    (heads padded with zeros; default vd)."""
     _cuda(a, gate, out)
     assert a.is_contiguous() and out.is_contiguous() and a.dtype in (out.dtype, torch.float32)
     assert gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1)
     _check(lib().vob_diff_heads_combine(_p(a), int(a.dtype == torch.float32), _p(gate), ctypes.c_long(gate_stride), _p(out),
                                         num_tokens, heads, group, vd, ctypes.c_float(lam), ctypes.c_float(post),
-                                        ctypes.c_float(eps), _code(out.dtype), _stream()), "diff_heads_combine")
+                                        ctypes.c_float(eps), _code(out.dtype), int(vd_norm or vd), _stream()), "diff_heads_combine")
 
 
 def layer_norm_step(stream, eps: float, err, y1=None, y2=None, w=None, b=None, out=None, rows=None, n_out: Optional[int] = None,

@@ -23,6 +23,12 @@ Options, each a parameter:
 
 q, k, v and the gate are one product.  The cache plane holds keys [pages, maps * kv_heads, page, dim] and values
 [pages, kv_heads, page, vdim]; a window or a chunk lets the cache manager give back the pages behind it.
+
+The tensor-core attention kernels hold ONE head size, a multiple of 16.  On the bfloat16 path a layer whose `dim` and `vdim`
+differ (or are no multiple of 16) therefore pads every head with zeros to one size (`PAD_HEADS`): zero rows are added to
+W_q, W_k, W_v and W_g and zero columns to W_o when the weights are loaded, so the products write padded heads by
+themselves, a padded query against a padded key is the same score, a padded value adds nothing, and the norms' means
+count a head's own elements only.  The cost is the cache and the products of the padding; the 32-bit path pads nothing.
 Tensors: <prefix>q, k, v, o (+ q.norm, k.norm; lq1, lk1, lq2, lk2; g).
 """
 from __future__ import annotations
@@ -36,6 +42,21 @@ from ..weights.loader import TensorSpec
 from .attention import paged_attend
 from .base import NO_ROTATION, CacheSpec, Mixer, register_part
 from .linear import linear
+
+
+# Whether bfloat16 layers pad their heads to one size that the tensor-core kernels take (else such layers run the plain kernel).
+PAD_HEADS = True
+
+
+def _pad_heads(t: torch.Tensor, size: int, to: int, dim: int = 0) -> torch.Tensor:
+    """`t` holds heads of `size` elements along `dim`; every head gets zeros behind it up to `to` elements."""
+    if size == to:
+        return t
+    t = t.movedim(dim, 0)
+    heads, rest = t.shape[0] // size, t.shape[1:]
+    out = t.new_zeros((heads, to) + tuple(rest))
+    out[:, :size] = t.reshape(heads, size, *rest)
+    return out.reshape(heads * to, *rest).movedim(0, dim)
 
 
 class CappedAttention(Mixer):
@@ -66,8 +87,13 @@ class CappedAttention(Mixer):
             raise ValueError(f"the position rule rotates {self.rotation.rotary_dim} dimensions, a head has {self.kd}")
         self.prefix, self.dtype, self.device = prefix, dtype, device
         self.group = self.nh // self.kvh
-        self.n_q, self.n_k = self.maps * self.nh * self.kd, self.maps * self.kvh * self.kd
-        self.n_v, self.n_o = self.kvh * self.vd, self.nh * self.vd
+        # kp, vp: a head's size as the products write it and the cache holds it
+        one = (max(self.kd, self.vd) + 15) // 16 * 16
+        padded = (PAD_HEADS and dtype == torch.bfloat16 and (self.kd != self.vd or self.kd % 16)
+                  and kernels.has_fast_attention(dtype, one, self.group) and self.scale > 0.0)
+        self.kp, self.vp = (one, one) if padded else (self.kd, self.vd)
+        self.n_q, self.n_k = self.maps * self.nh * self.kp, self.maps * self.kvh * self.kp
+        self.n_v, self.n_o = self.kvh * self.vp, self.nh * self.vp
         self.gate_off = self.n_q + self.n_k + self.n_v
         self.width = (self.gate_off + (self.n_o if self.gate else 0) + 7) // 8 * 8        # rows stay 16-byte aligned
         self.w_in = self.wo = self.wq_norm = self.wk_norm = None
@@ -77,14 +103,15 @@ class CappedAttention(Mixer):
     # ---- tensors
     def tensor_specs(self) -> List[TensorSpec]:
         p, D = self.prefix, self.H
-        specs = [TensorSpec(p + "q", (self.n_q, D), "matrix", D), TensorSpec(p + "k", (self.n_k, D), "matrix", D),
-                 TensorSpec(p + "v", (self.n_v, D), "matrix", D), TensorSpec(p + "o", (D, self.n_o), "matrix", self.n_o)]
+        n_q, n_k, n_v, n_o = (self.maps * self.nh * self.kd, self.maps * self.kvh * self.kd, self.kvh * self.vd, self.nh * self.vd)
+        specs = [TensorSpec(p + "q", (n_q, D), "matrix", D), TensorSpec(p + "k", (n_k, D), "matrix", D),
+                 TensorSpec(p + "v", (n_v, D), "matrix", D), TensorSpec(p + "o", (D, n_o), "matrix", n_o)]
         if self.row_norm:
-            specs += [TensorSpec(p + "q.norm", (self.n_q,), "norm"), TensorSpec(p + "k.norm", (self.n_k,), "norm")]
+            specs += [TensorSpec(p + "q.norm", (n_q,), "norm"), TensorSpec(p + "k.norm", (n_k,), "norm")]
         if self.maps == 2:
             specs += [TensorSpec(p + n, (self.kd,), "coefficient", init="small") for n in ("lq1", "lk1", "lq2", "lk2")]
         if self.gate:
-            specs.append(TensorSpec(p + "g", (self.n_o, D), "matrix", D))
+            specs.append(TensorSpec(p + "g", (self.nh * self.vd, D), "matrix", D))
         return specs
 
     def _by_map(self, t: torch.Tensor) -> torch.Tensor:
@@ -96,17 +123,19 @@ class CappedAttention(Mixer):
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         p = self.prefix
-        rows = [self._by_map(tensors[p + "q"]), tensors[p + "k"], tensors[p + "v"]]
+        kd, kp, vd, vp = self.kd, self.kp, self.vd, self.vp
+        rows = [_pad_heads(self._by_map(tensors[p + "q"]), kd, kp), _pad_heads(tensors[p + "k"], kd, kp),
+                _pad_heads(tensors[p + "v"], vd, vp)]
         if self.gate:
-            rows.append(tensors[p + "g"])
+            rows.append(_pad_heads(tensors[p + "g"], vd, vp))
         pad = self.width - sum(r.shape[0] for r in rows)
         if pad:
             rows.append(rows[0].new_zeros((pad, self.H)))
         self.w_in = torch.cat(rows, dim=0).contiguous()
-        self.wo = tensors[p + "o"].contiguous()
+        self.wo = _pad_heads(tensors[p + "o"], vd, vp, dim=1).contiguous()
         if self.row_norm:
-            self.wq_norm = self._by_map(tensors[p + "q.norm"]).contiguous()
-            self.wk_norm = tensors[p + "k.norm"].contiguous()
+            self.wq_norm = _pad_heads(self._by_map(tensors[p + "q.norm"]), kd, kp).contiguous()
+            self.wk_norm = _pad_heads(tensors[p + "k.norm"], kd, kp).contiguous()
         if self.maps == 2:
             f = lambda n: tensors[p + n].to(torch.float32)
             lam = torch.exp((f("lq1") * f("lk1")).sum()) - torch.exp((f("lq2") * f("lk2")).sum()) + self.diff
@@ -115,7 +144,7 @@ class CappedAttention(Mixer):
             self._pairs = kernels.decode_pairs_counter(self.wo.device)
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(self.maps * self.kvh, self.kd, self.window, value_heads=self.kvh, value_dim=self.vd, chunk=self.chunk)
+        return CacheSpec(self.maps * self.kvh, self.kp, self.window, value_heads=self.kvh, value_dim=self.vp, chunk=self.chunk)
 
     # ---- one step
     def forward(self, x, ctx, cache, state=None, write_cache: bool = True):
@@ -123,15 +152,16 @@ class CappedAttention(Mixer):
         nh, kvh = self.maps * self.nh, self.maps * self.kvh
         qkv = linear(x, self.w_in, ctx.ws.get("qkvg", T, self.width, x.dtype), ctx)
         kernels.rownorm_rope_kv_write(qkv, ctx.positions, ctx.slot_mapping[cache.group], self.wq_norm, self.wk_norm,
-                                      self.rotation, cache.k, cache.v, T, nh, kvh, self.kd, self.eps, write_cache, ctx.err)
+                                      self.rotation, cache.k, cache.v, T, nh, kvh, self.kp, self.eps, write_cache, ctx.err,
+                                      kd_norm=self.kd)
         # two maps are subtracted before anything rounds them: their outputs stay float
-        a = ctx.ws.get("attn_maps", T, nh * self.vd, torch.float32 if self.maps == 2 else x.dtype)
-        paged_attend(qkv, self.width, a, cache.k, cache.v, cache.group, ctx, T, nh, kvh, self.kd, self.window, self.scale,
+        a = ctx.ws.get("attn_maps", T, nh * self.vp, torch.float32 if self.maps == 2 else x.dtype)
+        paged_attend(qkv, self.width, a, cache.k, cache.v, cache.group, ctx, T, nh, kvh, self.kp, self.window, self.scale,
                      self._pairs, softcap=self.softcap, chunk=self.chunk)
         if self.maps == 2:
             heads = ctx.ws.get("attn_out", T, self.n_o, x.dtype)
             kernels.diff_heads_combine(a, qkv[:, self.gate_off:] if self.gate else None, self.width, heads, T, self.nh,
-                                       self.group, self.vd, self.lam, 1.0 - self.diff, self.eps)
+                                       self.group, self.vp, self.lam, 1.0 - self.diff, self.eps, vd_norm=self.vd)
         else:
             heads = a
         return linear(heads, self.wo, ctx.ws.get("attn_proj", T, self.H, x.dtype), ctx)
