@@ -102,6 +102,7 @@ def as_held(w, dtype):
 
 
 CLOSE_CALL = 0.02     # a router's choice that scores moved by this much would turn over is not held against bfloat16
+TIE = 1e-6            # ... and one that this much would turn over not against 32 bits either
 
 
 class Rows(np.ndarray):
@@ -117,7 +118,12 @@ def plain_logits(cfg, w, tokens):
     margins = []
     exact = P.forward(cfg, w, tokens, torch.float64, margins=margins).numpy()
     out = exact.view(Rows)
-    out.unsure = (torch.stack(margins).min(0).values.numpy() < CLOSE_CALL) if margins else np.zeros(len(tokens), bool)
+    least = torch.stack(margins).min(0).values.numpy() if margins else np.ones(len(tokens))
+    out.unsure = least < CLOSE_CALL
+    # a tie in 32 bits (two scores that only float64 tells apart, as where both sigmoids are all but 1): from that row on
+    # the two runs may have taken different experts, and later rows read what that row left
+    ties = np.nonzero(least < TIE)[0]
+    out.sure_rows = int(ties[0]) if len(ties) else len(tokens)
     rounded = P.forward(cfg, w, tokens, torch.float64, noise=to_16_bits).numpy()
     out.moved = np.sqrt(((rounded - exact) ** 2).mean(-1)) / exact.std(-1)
     return out
@@ -160,11 +166,15 @@ def close(got, want, dtype, what):
     """float32: within 1e-4 of the logits' spread, row by row (rounding alone stays near 1e-6; a wrong key, gate, expert or
     mask moves a row by percents).  bfloat16: within 0.1 of it, wider where the plain run itself moves when its sublayers
     round to 16 bits, and except for rows where the plain run says that a router's choice was a close call."""
-    unsure, moved = getattr(want, "unsure", None), getattr(want, "moved", None)
+    unsure, moved, sure_rows = getattr(want, "unsure", None), getattr(want, "moved", None), getattr(want, "sure_rows", None)
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     assert got.shape == want.shape, what
     err = np.sqrt(((got - want) ** 2).mean(-1)) / want.std(-1)
     if dtype == "float32":
+        if sure_rows is not None and len(unsure) == len(err):
+            err = err[:sure_rows]
+        if len(err) == 0:
+            return
         assert err.max() < 1e-4, f"{what}: row {int(err.argmax())} is {err.max():.3e} of the spread off"
         return
     sure = np.ones(len(err), bool) if unsure is None or len(unsure) != len(err) else ~unsure
@@ -274,6 +284,58 @@ def test_unequal_requests_in_one_batch_over_pages_used_again(folders, name, dtyp
     assert free_pages() == free_at_start, "every page came back"
     for rid, toks in reqs.items():
         close(np.concatenate(got[rid], 0), truth(folders, name, toks, dtype), dtype, f"{name} {dtype} request {rid} in mixed batches")
+
+
+def random_configuration(seed):
+    """A configuration drawn from a seeded generator: two to four layers of either kind in any order, head counts, key and
+    value sizes (equal, unequal, multiples of 16 or not), masks shorter and longer than a page, any part of a head
+    rotated, every kind of feed-forward, a loop or none."""
+    rng = random.Random(seed)
+    layers = []
+    for _ in range(rng.randint(2, 4)):
+        kv = rng.choice([1, 2, 3])
+        heads = kv * rng.choice([1, 2, 4])
+        dim = rng.choice([8, 16, 24, 32, 48, 64])
+        vdim = rng.choice([dim, dim, 2 * dim, rng.choice([8, 16, 40, 64])])
+        size, scale, cap = rng.choice([1, 5, 16, 23, 64, 100, 400]), rng.choice([0.05, 0.15, 0.3]), rng.choice([0.0, 4.0, 20.0, 50.0])
+        if rng.random() < 0.5:
+            layer = _two_map(heads, kv, dim, vdim, size, rng.choice([0.1, 0.4, 0.7]), scale, cap)
+        else:
+            layer = _windowed(heads, kv, dim, vdim, size, rng.choice([0, 2, dim // 2, dim]), rng.choice([100.0, 1e4, 1e6]), scale, cap)
+        kind = rng.choice(["none", "dense", "moe", "moe"])
+        if kind == "none":
+            layer = _none(layer)
+        elif kind == "dense":
+            layer = _dense(layer, rng.choice([24, 64, 100]))
+        else:
+            count = rng.choice([None, 1, 2, 3])
+            per = rng.choice([1, 2, 3])
+            experts = (count or 1) * per if count else rng.choice([3, 5, 8])
+            keep = rng.randint(1, count) if count else None
+            top = rng.randint(1, max(1, min(3, per * keep if count else experts)))
+            layer = _moe(layer, rng.choice([8, 24, 40]), experts, top, count, keep, rng.choice([1.0, 2.5]))
+        layers.append(layer)
+    cfg = {"architecture": "Rakizen", "vocab": rng.choice([61, 128, 300]), "width": rng.choice([32, 48, 72, 128]),
+           "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers}
+    if rng.random() < 0.6:
+        start = rng.randint(0, len(layers) - 1)
+        cfg["loop"] = {"start": start, "stop": rng.randint(start + 1, len(layers)), "times": rng.randint(1, 3)}
+    return cfg, rng.choice([16, 32, 64])
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_configurations(seed, tmp_path):
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    cfg, page = random_configuration(1000 + seed)
+    dirs = random_folders(tmp_path, cfg, seed)
+    g = torch.Generator().manual_seed(seed)
+    toks = torch.randint(0, cfg["vocab"], (140,), generator=g).tolist()
+    for dtype in DTYPES:
+        c, w = P.read_folder(dirs[dtype])
+        want = plain_logits(c, as_held(w, dtype), toks)
+        r = TraceRunner(dirs[dtype], dtype, 192, page, max_live=2)
+        for cuts in ([len(toks)], [len(toks) - 30] + [1] * 30, [3, 1, 17, 2, 40]):
+            close(feed(r, "x", toks, cuts), want, dtype, f"random configuration {seed}, {dtype}, cuts {cuts[:5]}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
