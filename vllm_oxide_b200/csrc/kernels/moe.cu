@@ -38,43 +38,68 @@ __device__ __forceinline__ Best warp_best(Best x) {
 
 constexpr int ROUTE_NT = 256;
 
+constexpr int ROUTE_TOKENS = 4;   // tokens a block: the router's rows are read once for all of them
+
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_NT)
 moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __restrict__ correction, int* ids, float* weights,
-                 int W, int E, int top, int count, int keep, int sigmoid_scores, int group_top, int normalise, float weight_scale) {
+                 int W, int E, int top, int count, int keep, int sigmoid_scores, int group_top, int normalise, float weight_scale,
+                 int num_tokens, int per_block) {
   extern __shared__ __align__(16) float route_smem[];
-  float* hrow = route_smem;          // [W]
-  float* score = hrow + W;           // [E] softmax
-  float* choice = score + E;         // [E] score + correction, -inf once taken or shut out
-  float* gbest = choice + E;         // [count]
+  float* hrows = route_smem;                        // [per_block][W]
+  float* lists = hrows + (size_t)per_block * W;     // per token: [E] scores, [E] choice scores, [count] group scores
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int d = threadIdx.x; d < W; d += ROUTE_NT) hrow[d] = to_f<T>(h[(size_t)t * W + d]);
+  const int t0 = blockIdx.x * per_block, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int here = min(per_block, num_tokens - t0);
+  for (int d = threadIdx.x; d < here * W; d += ROUTE_NT) hrows[d] = to_f<T>(h[(size_t)t0 * W + d]);
   __syncthreads();
   // a warp takes experts warp, warp + 8, ...; a lane sums four elements at a time into four chains (one chain where the
-  // width is no multiple of 4): the order of a logit's additions depends on the width alone
+  // width is no multiple of 4): the order of a logit's additions depends on the width alone, not on the tokens beside it
   const bool vec = W % 4 == 0 && ((uintptr_t)w_router % 16) == 0;
   for (int e = warp; e < E; e += ROUTE_NT / 32) {
     const float* wr = w_router + (size_t)e * W;
-    float z = 0.f;
+    float z[ROUTE_TOKENS];
     if (vec) {
-      float z4[4] = {0.f, 0.f, 0.f, 0.f};
+      float z4[ROUTE_TOKENS][4];
+#pragma unroll
+      for (int k = 0; k < ROUTE_TOKENS; ++k) z4[k][0] = z4[k][1] = z4[k][2] = z4[k][3] = 0.f;
       for (int d = lane * 4; d < W; d += 128) {
         const float4 wv = *reinterpret_cast<const float4*>(wr + d);
-        const float4 hv = *reinterpret_cast<const float4*>(hrow + d);
-        z4[0] = fmaf(hv.x, wv.x, z4[0]); z4[1] = fmaf(hv.y, wv.y, z4[1]);
-        z4[2] = fmaf(hv.z, wv.z, z4[2]); z4[3] = fmaf(hv.w, wv.w, z4[3]);
+#pragma unroll
+        for (int k = 0; k < ROUTE_TOKENS; ++k) {
+          if (k < here) {
+            const float4 hv = *reinterpret_cast<const float4*>(hrows + (size_t)k * W + d);
+            z4[k][0] = fmaf(hv.x, wv.x, z4[k][0]); z4[k][1] = fmaf(hv.y, wv.y, z4[k][1]);
+            z4[k][2] = fmaf(hv.z, wv.z, z4[k][2]); z4[k][3] = fmaf(hv.w, wv.w, z4[k][3]);
+          }
+        }
       }
-      z = (z4[0] + z4[1]) + (z4[2] + z4[3]);
+#pragma unroll
+      for (int k = 0; k < ROUTE_TOKENS; ++k) z[k] = (z4[k][0] + z4[k][1]) + (z4[k][2] + z4[k][3]);
     } else {
-      for (int d = lane; d < W; d += 32) z = fmaf(hrow[d], wr[d], z);
+#pragma unroll
+      for (int k = 0; k < ROUTE_TOKENS; ++k) z[k] = 0.f;
+      for (int d = lane; d < W; d += 32) {
+        const float wv = wr[d];
+#pragma unroll
+        for (int k = 0; k < ROUTE_TOKENS; ++k)
+          if (k < here) z[k] = fmaf(hrows[(size_t)k * W + d], wv, z[k]);
+      }
     }
-    z = warp_sum(z);
-    if (lane == 0) score[e] = z;
+#pragma unroll
+    for (int k = 0; k < ROUTE_TOKENS; ++k) {
+      const float sum = warp_sum(z[k]);
+      if (lane == 0 && k < here) lists[(size_t)k * (2 * E + count) + e] = sum;
+    }
   }
   __syncthreads();
-  if (warp != 0) return;
+  // warp k chooses for token k
+  if (warp >= here) return;
+  const int t = t0 + warp;
+  float* score = lists + (size_t)warp * (2 * E + count);   // [E] softmax or sigmoid
+  float* choice = score + E;                               // [E] score + correction, -inf once taken or shut out
+  float* gbest = choice + E;                               // [count]
   if (sigmoid_scores) {
     for (int e = lane; e < E; e += 32) {
       const float s = 1.f / (1.f + expf(-score[e]));
@@ -425,14 +450,19 @@ VOB_API int vob_moe_route(const void* h, const float* w_router, const float* cor
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || count <= 0 || E % count || keep <= 0 || keep > count || (long)(E / count) * keep < top)
     return VOB_BAD_ARGUMENT;
-  const size_t smem = (size_t)(W + 2 * E + count) * sizeof(float);
+  // as many tokens a block as 96 KB hold (up to ROUTE_TOKENS) while the blocks still fill the device twice; one where the
+  // width is no multiple of 4 (rows stay aligned).  A token's arithmetic does not depend on how many share its block.
+  int per_block = (int)std::min<long>(ROUTE_TOKENS, std::max<long>(1, T / (2L * sm_count())));
+  while (per_block > 1 && ((size_t)per_block * (W + 2 * E + count) * sizeof(float) > 96 * 1024 || W % 4)) --per_block;
+  const size_t smem = (size_t)per_block * (W + 2 * E + count) * sizeof(float);
   if (smem > 200 * 1024) return VOB_UNSUPPORTED;
 #define VOB_ROUTE(TYPE)                                                                                                  \
   do {                                                                                                                   \
     if (smem > 48 * 1024)                                                                                                \
       cudaFuncSetAttribute(moe_route_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
-    return launch_kernel(moe_route_kernel<TYPE>, dim3(T), ROUTE_NT, smem, stream, (const TYPE*)h, w_router, correction, ids, \
-                         weights, W, E, top, count, keep, sigmoid_scores, group_top, normalise, weight_scale);          \
+    return launch_kernel(moe_route_kernel<TYPE>, dim3((T + per_block - 1) / per_block), ROUTE_NT, smem, stream,          \
+                         (const TYPE*)h, w_router, correction, ids, weights, W, E, top, count, keep, sigmoid_scores,     \
+                         group_top, normalise, weight_scale, T, per_block);                                              \
   } while (0)
   if (dtype == VOB_F32) VOB_ROUTE(float);
   if (dtype == VOB_BF16) VOB_ROUTE(__nv_bfloat16);
