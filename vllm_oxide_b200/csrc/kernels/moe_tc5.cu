@@ -151,18 +151,28 @@ moe_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         float v[32];
         t5_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * MT_NT + c0), v);
         const int tok = row_token[mt * MT_NT + c0 + lane];        // lane j's entry belongs to column c0 + j
+        if (EPI == MT_EPI_SILU_PAIRS_BF16) {
+          // Two lanes hold a (gate, up) pair of features.  They finish two token columns at a time, the even lane column
+          // j and the odd lane column j + 1, so every lane takes one exponential for two columns and one exchange
+          // serves both.
+          const bool odd = lane & 1;
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const bool live0 = __shfl_sync(0xffffffffu, tok, j) >= 0, live1 = __shfl_sync(0xffffffffu, tok, j + 1) >= 0;
+            if (!live0 && !live1) continue;                       // the same for every lane of the warp
+            const float got = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[j + 1], 1);
+            const float gate = odd ? got : v[j], up = odd ? v[j + 1] : got;
+            if ((odd ? live1 : live0) && (n | 1) < N) {
+              const long m = (long)mt * MT_NT + c0 + j + (odd ? 1 : 0);
+              reinterpret_cast<__nv_bfloat16*>(out)[m * ldo + (n >> 1)] =
+                  __float2bfloat16_rn(__fdividef(gate, 1.f + __expf(-gate)) * up);
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const bool live = __shfl_sync(0xffffffffu, tok, j) >= 0;
-          if (EPI == MT_EPI_SILU_PAIRS_BF16) {
-            if (!live) continue;                                  // the same for every lane of the warp
-            const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
-            if (!(lane & 1) && n + 1 < N) {
-              const long m = (long)mt * MT_NT + c0 + j;
-              reinterpret_cast<__nv_bfloat16*>(out)[m * ldo + n / 2] = __float2bfloat16_rn(v[j] / (1.f + __expf(-v[j])) * up);
-            }
-            continue;
-          }
           if (live && n < N) {
             const long m = (long)mt * MT_NT + c0 + j;
             if (EPI == MT_EPI_F32) {
