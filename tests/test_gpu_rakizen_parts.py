@@ -116,6 +116,15 @@ CASES = {
     "window, 64 wide": ("attention_2", 64, dict(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.4, softcap=20.0, mask={"size": 70},
                                                 rot={"dims": 32, "base": 1e6})),
 }
+# Key and value sizes that the bfloat16 path pads to every other multiple of 16 up to 256 (the tensor-core kernels are
+# compiled for one head size each), two maps and windows in turn.
+for _i, (_d, _e) in enumerate([(100, 200), (72, 144), (110, 110), (150, 75), (170, 96), (220, 64), (230, 230), (90, 96), (250, 256)]):
+    if _i % 2:
+        CASES[f"padded {_d}/{_e}"] = ("attention_2", 40, dict(heads=2, kv_heads=1, dim=_d, vdim=_e, scale=_d ** -0.5, softcap=11.0,
+                                                            mask={"size": 41 + _i}, rot={"dims": 2 * (_d // 4), "base": 3e3}))
+    else:
+        CASES[f"padded {_d}/{_e}"] = ("attention", 40, dict(heads=2, kv_heads=2, dim=_d, vdim=_e, diff=0.25, scale=_d ** -0.5,
+                                                          softcap=14.0, mask={"size": 37 + _i}))
 
 
 @pytest.mark.parametrize("dt", DTYPES)
