@@ -53,6 +53,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 1 / x by the hardware approximation (1 ulp; +inf gives 0).
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // What a head's softmax does besides scaling and the causal mask, and what may come after it.  `sink`: the softmax has a
 // silent extra entry of score 0 that has no value; it adds 2^(0 - M) to a denominator that is taken relative to M (scores in
 // the base-2 domain).  `gate`: head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]).  `cap_out` > 0: a
@@ -90,9 +97,7 @@ __device__ __forceinline__ int first_key(int pos, int window, const HeadEpilogue
 // (the tanh approximation of the hardware is good to 2^-11 only, which a cap of 30 would turn into 1% of a weight).
 __device__ __forceinline__ float score2(float raw, float sc, const HeadEpilogue& ep) {
   if (ep.cap_out > 0.f) {
-    float e;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(raw * ep.cap_in));
-    return fmaf(-2.f * ep.cap_out, __fdividef(1.f, 1.f + e), ep.cap_out);
+    return fmaf(-2.f * ep.cap_out, fast_rcp(1.f + fast_exp2(raw * ep.cap_in)), ep.cap_out);
   }
   return raw * sc;
 }

@@ -357,7 +357,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         for (int c = 0; c < 64; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
         if (ep.cap_out > 0.f) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) s[c] = fmaf(cap_raw2, __fdividef(1.f, 1.f + fast_exp2(s[c] * ep.cap_in)), cap_raw);
+          for (int c = 0; c < 64; ++c) s[c] = fmaf(cap_raw2, fast_rcp(1.f + fast_exp2(s[c] * ep.cap_in)), cap_raw);
         }
         if (need_mask) {
 #pragma unroll
