@@ -19,11 +19,32 @@ namespace vob {
 
 constexpr int PN_NT = 256;
 
+// Four neighbouring elements of the model's type as floats, by one access.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(PN_NT)
 layer_norm_step_kernel(float* stream, const T* y1, const T* y2, const float* __restrict__ w, const float* __restrict__ b,
-                       T* out, const int* __restrict__ rows, int num_src_rows, int D, float eps, int init, int* err) {
-  extern __shared__ float pn_row[];    // [D] the new row
+                       T* out, const int* __restrict__ rows, int num_src_rows, int D, float eps, int init, int* err, int wide) {
+  extern __shared__ __align__(16) float pn_row[];    // [D] the new row
   __shared__ float scratch[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -39,6 +60,46 @@ layer_norm_step_kernel(float* stream, const T* y1, const T* y2, const float* __r
   const size_t base = (size_t)src * D;
   const bool changed = init || y1 || y2;
   const bool store = rows == nullptr && changed;
+  if (wide) {
+    // widths that are a multiple of 4 (every pointer 16-byte aligned): a thread takes four neighbours an access; the order
+    // of a row's additions still depends on its width alone
+    float sum = 0.f;
+    for (int d = threadIdx.x * 4; d < D; d += PN_NT * 4) {
+      float x[4] = {0.f, 0.f, 0.f, 0.f}, a[4], c[4];
+      if (!init) load4(stream + base + d, x);
+      if (y1) load4(y1 + base + d, a);
+      if (y2) load4(y2 + base + d, c);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (y1 && y2) x[i] += a[i] + c[i];
+        else if (y1) x[i] += a[i];
+        else if (y2) x[i] += c[i];
+        sum += x[i];
+      }
+      if (store) store4(stream + base + d, x);
+      store4(pn_row + d, x);
+    }
+    if (!out) return;
+    const float mean = block_sum<PN_NT>(sum, scratch) / (float)D;
+    float sq = 0.f;
+    for (int d = threadIdx.x * 4; d < D; d += PN_NT * 4) {
+      float x[4];
+      load4(pn_row + d, x);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float c = x[i] - mean; sq = fmaf(c, c, sq); }
+    }
+    const float inv = 1.f / sqrtf(block_sum<PN_NT>(sq, scratch) / (float)D + eps);
+    for (int d = threadIdx.x * 4; d < D; d += PN_NT * 4) {
+      float x[4], g[4], o[4], bias[4] = {0.f, 0.f, 0.f, 0.f};
+      load4(pn_row + d, x);
+      load4(w + d, g);
+      if (b) load4(b + d, bias);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] = (x[i] - mean) * inv * g[i] + bias[i];
+      store4(out + (size_t)r * D + d, o);
+    }
+    return;
+  }
   float sum = 0.f;
   for (int d = threadIdx.x; d < D; d += PN_NT) {
     float x = init ? 0.f : stream[base + d];
@@ -76,12 +137,13 @@ VOB_API int vob_layer_norm_step(float* stream, const void* y1, const void* y2, c
   if (D <= 0 || (rows && !out) || (out && !w)) return VOB_BAD_ARGUMENT;
   const size_t smem = (size_t)D * sizeof(float);
   if (smem > 200 * 1024) return VOB_UNSUPPORTED;
+  const int wide = D % 4 == 0 && (((uintptr_t)stream | (uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)w | (uintptr_t)b | (uintptr_t)out) & 15) == 0;
 #define VOB_PN_LAUNCH(TYPE)                                                                                             \
   do {                                                                                                                  \
     if (smem > 48 * 1024)                                                                                               \
       cudaFuncSetAttribute(layer_norm_step_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
     return launch_kernel(layer_norm_step_kernel<TYPE>, dim3(n_out), PN_NT, smem, stream_, stream, (const TYPE*)y1,      \
-                         (const TYPE*)y2, w, b, (TYPE*)out, rows, num_src_rows, D, eps, init, err);                     \
+                         (const TYPE*)y2, w, b, (TYPE*)out, rows, num_src_rows, D, eps, init, err, wide);                     \
   } while (0)
   if (dtype == VOB_F32) VOB_PN_LAUNCH(float);
   if (dtype == VOB_BF16) VOB_PN_LAUNCH(__nv_bfloat16);
