@@ -2,7 +2,7 @@
 
 Every plane (a layer's cache) says through its `CacheSpec` what it stores a token: keys and values, or one
 tensor; how wide; for all positions or a window; in pages of how many tokens; in which dtype.  Planes with the
-same window (or chunk) and page size form a cache group: one page pool and one block table per request, managed on the
+same window (or chunk), kept first positions and page size form a cache group: one page pool and one block table per request, managed on the
 host by `KvCacheManager` (C++).  The reference keeps one buffer [2, layers, num_blocks, block_size, kv_heads,
 head_dim] (vllm-oxide, crates/vllm-oxide/src/attention/mod.rs:42-85); here every plane has a [tensors, num_pages,
 kv_heads, block_size, head_dim] buffer: planes of different widths can share a group, and the keys of one head
@@ -30,6 +30,7 @@ class CacheGroup:
     num_blocks: int
     planes: List[int]
     chunk: int = 0
+    keep_first: int = 0
 
 
 class PagedCache:
@@ -39,15 +40,16 @@ class PagedCache:
         self.dtype, self.device, self.block_size = dtype, device, block_size
         for s in cache_specs:
             if s is not None and (s.tensors not in (1, 2) or s.kv_heads <= 0 or s.head_dim <= 0 or s.window < 0 or s.chunk < 0
+                                  or s.keep_first < 0
                                   or (s.block_size is not None and s.block_size <= 0)
                                   or ((s.value_heads or s.value_dim) and s.tensors != 2) or min(s.value_shape()) <= 0):
                 raise ValueError(f"unusable cache spec {s}")
         page_size = lambda s: s.block_size or block_size
-        key_of = lambda s: (s.window, s.chunk, page_size(s))
+        key_of = lambda s: (s.window, s.chunk, page_size(s), s.keep_first if (s.window or s.chunk) else 0)
         keys = sorted({key_of(s) for s in cache_specs if s is not None})
         if not keys:
-            keys = [(0, 0, block_size)]   # a model without paged keys still gets block tables (of a pool nobody reads)
-        self.groups: List[CacheGroup] = [CacheGroup(w, bs, 0, [], c) for w, c, bs in keys]
+            keys = [(0, 0, block_size, 0)]   # a model without paged keys still gets block tables (of a pool nobody reads)
+        self.groups: List[CacheGroup] = [CacheGroup(w, bs, 0, [], c, k) for w, c, bs, k in keys]
         for plane, s in enumerate(cache_specs):
             if s is not None:
                 self.groups[keys.index(key_of(s))].planes.append(plane)
@@ -86,7 +88,7 @@ class PagedCache:
             None if s is None else torch.zeros((num_state_slots, *s.shape), dtype=s.dtype, device=device)
             for s in state_specs]
         self.manager = host.KvCacheManager(
-            [host.GroupSpec(g.block_size, g.num_blocks, g.window, g.chunk) for g in self.groups], num_state_slots,
+            [host.GroupSpec(g.block_size, g.num_blocks, g.window, g.chunk, g.keep_first) for g in self.groups], num_state_slots,
             # state of fixed size is not snapshotted at page boundaries: with such a layer nothing is skipped on a hit
             prefix_caching and not any(s is not None for s in state_specs))
 

@@ -504,3 +504,119 @@ class RakizenConfig:
         if self.loop is not None:
             d["loop"] = {"start": self.loop[0], "stop": self.loop[1], "times": self.loop[2]}
         return d
+
+
+# ---------------------------------------------------------------------------------------------------------------
+_DEPOLIX_MIXERS = ("latent_attention", "parallel")
+
+
+def _count(d: dict, key: str, where: str, default: int = 0) -> int:
+    """A whole number that may be zero."""
+    v = d.get(key, default)
+    if v is None:
+        return default
+    if isinstance(v, bool) or not isinstance(v, int) or v < 0:
+        raise ConfigError(f"{where}: '{key}' must be a whole number that is not negative, got {v!r}")
+    return v
+
+
+@dataclass(frozen=True)
+class DepolixLayer:
+    type: str                   # "latent_attention" | "parallel"
+    mixer: dict                 # the mixer's sizes and constants, as config.json gives them
+    mlp: Optional[dict]         # None, {"kind": "dense", "ff", "limit"} or {"kind": "moe", "expert": {"ff", "limit"}, "router": {...}}
+
+
+@dataclass(frozen=True)
+class DepolixConfig:
+    """Depolix: a decoder whose layers are listed one by one in config.json.  A layer has ONE RMS norm with a gain stored
+    around zero that its mixer and its feed-forward both read; m times the sum of their outputs is added to one float
+    residual stream (`residual_mult`).  The mixer is `latent_attention` (low-rank queries; one latent and one rotated key
+    part a token; rotation of halves with stretched frequencies; an output gate an element) or `parallel`: `left`,
+    attention behind short convolutions with unit-RMS q and k, a learned bias by distance, a window that keeps the first
+    tokens and a gate a head, beside `right`, a gated delta rule with a decay per head and key channel; each side is normed
+    over the width and the result is half their sum.  The feed-forward is a clamped gated layer with biases, a mixture of
+    such experts weighted by the softmax over the chosen logits, or absent.  Keys: `vocab`, `width`, `norm.eps`,
+    `embedding.scale`, `residual_mult`, `logit_scale`, `layers[i]` = {type, mixer{...}, mlp}.  There is no largest position."""
+    vocab: int
+    width: int
+    eps: float
+    layers: tuple
+    embedding_scale: float = 1.0
+    residual_mult: float = 1.0
+    logit_scale: float = 1.0
+    torch_dtype: str = "bfloat16"
+
+    architecture = "Depolix"
+
+    @staticmethod
+    def _check_latent(m: dict, w: str) -> None:
+        for k in ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank"):
+            _need(m, k, int, w)
+        _need(m, "scale", float, w)
+        rot = _sub(m, "rot", w)
+        _need(rot, "base", float, w + ".rot")
+        dims = rot.get("dims")
+        if isinstance(dims, bool) or not isinstance(dims, int) or dims < 0 or dims % 2 or dims > m["rot_dim"]:
+            raise ConfigError(f"{w}: rot.dims {dims!r} must be even and between 0 and rot_dim {m['rot_dim']}")
+        if rot.get("scaling") is not None:
+            s = _sub(rot, "scaling", w + ".rot")
+            for k in ("factor", "original", "fast", "slow"):
+                if _need(s, k, float, w + ".rot.scaling") <= 0:
+                    raise ConfigError(f"{w}: rot.scaling.{k} must be positive")
+
+    @staticmethod
+    def _check_side(m: dict, w: str) -> None:
+        for k in ("heads", "kv_heads", "dim", "vdim", "conv"):
+            _need(m, k, int, w)
+        if m["heads"] % m["kv_heads"]:
+            raise ConfigError(f"{w}: heads {m['heads']} is not a multiple of kv_heads {m['kv_heads']}")
+
+    @classmethod
+    def from_dict(cls, d: dict, where: str = "config.json") -> "DepolixConfig":
+        layers = d.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError(f"{where}: 'layers' must be a non-empty list")
+        out = []
+        for i, layer in enumerate(layers):
+            w = f"{where}: layers[{i}]"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"{w} must be an object")
+            kind = layer.get("type")
+            if kind not in _DEPOLIX_MIXERS:
+                raise ConfigError(f"{w}: type {kind!r} is not one of {list(_DEPOLIX_MIXERS)}")
+            m = _sub(layer, "mixer", w)
+            if kind == "latent_attention":
+                cls._check_latent(m, w)
+            else:
+                left, right = _sub(m, "left", w), _sub(m, "right", w)
+                cls._check_side(left, w + ".left")
+                cls._check_side(right, w + ".right")
+                _need(left, "scale", float, w + ".left")
+                if left.get("mask") is not None:
+                    mask = _sub(left, "mask", w + ".left")
+                    _need(mask, "size", int, w + ".left.mask")
+                    _count(mask, "keep_first", w + ".left.mask")
+                if left.get("bias_max") is not None:
+                    _need(left, "bias_max", float, w + ".left")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                _check_moe(mlp, w)
+                if _need(mlp if mlp["kind"] == "dense" else mlp["expert"], "limit", float, w + ".mlp") <= 0:
+                    raise ConfigError(f"{w}: the feed-forward's limit must be positive")
+            out.append(DepolixLayer(kind, dict(m), None if mlp is None else dict(mlp)))
+        dtype = d.get("torch_dtype", d.get("dtype", "bfloat16"))
+        if not isinstance(dtype, str) or dtype not in _DTYPE_NAMES:
+            raise ConfigError(f"{where}: torch_dtype {dtype!r} is not one of {sorted(set(_DTYPE_NAMES))}")
+        number = lambda key, sub=None: (float((d.get(sub) or {}).get(key, 1.0)) if sub else float(d.get(key, 1.0)))
+        return cls(vocab=_need(d, "vocab", int, where), width=_need(d, "width", int, where),
+                   eps=_need(_sub(d, "norm", where), "eps", float, where + ".norm"), layers=tuple(out),
+                   embedding_scale=number("scale", "embedding"), residual_mult=number("residual_mult"),
+                   logit_scale=number("logit_scale"), torch_dtype=_DTYPE_NAMES[dtype])
+
+    def to_dict(self) -> dict:
+        return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.eps},
+                "embedding": {"scale": self.embedding_scale}, "residual_mult": self.residual_mult,
+                "logit_scale": self.logit_scale,
+                "layers": [{"type": l.type, "mixer": dict(l.mixer), "mlp": None if l.mlp is None else dict(l.mlp)}
+                           for l in self.layers]}

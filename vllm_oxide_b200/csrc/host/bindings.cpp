@@ -41,9 +41,11 @@ PYBIND11_MODULE(_host, m) {
       .def("free_order", &BlockPool::free_order);
 
   py::class_<GroupSpec>(m, "GroupSpec")
-      .def(py::init([](int block_size, int num_blocks, int window, int chunk) {
-        GroupSpec g; g.block_size = block_size; g.num_blocks = num_blocks; g.window = window; g.chunk = chunk; return g;
-      }), py::arg("block_size"), py::arg("num_blocks"), py::arg("window") = 0, py::arg("chunk") = 0)
+      .def(py::init([](int block_size, int num_blocks, int window, int chunk, int keep_first) {
+        GroupSpec g; g.block_size = block_size; g.num_blocks = num_blocks; g.window = window; g.chunk = chunk;
+        g.keep_first = keep_first; return g;
+      }), py::arg("block_size"), py::arg("num_blocks"), py::arg("window") = 0, py::arg("chunk") = 0, py::arg("keep_first") = 0)
+      .def_readwrite("keep_first", &GroupSpec::keep_first)
       .def_readwrite("block_size", &GroupSpec::block_size)
       .def_readwrite("num_blocks", &GroupSpec::num_blocks)
       .def_readwrite("window", &GroupSpec::window)

@@ -28,7 +28,10 @@ struct GroupSpec {
   int num_blocks = 1;
   int window = 0;  // 0: every key is kept; W > 0: only positions > query - W are read
   int chunk = 0;   // C > 0: a query reads only positions of its own block of C positions (blocks counted from 0)
+  int keep_first = 0;  // K > 0: positions below K stay readable whatever the window or block: their pages are never given back
   bool limited() const { return window > 0 || chunk > 0; }
+  // Pages [0, kept_pages()) hold kept first positions.
+  int kept_pages() const { return keep_first > 0 ? (keep_first + block_size - 1) / block_size : 0; }
   // The lowest position that a query at a position >= next can still read.
   int first_needed(int next) const {
     int lo = 0;
@@ -46,7 +49,7 @@ class KvCacheManager {
     if (num_state_slots <= 0) throw PoolError("KvCacheManager: at least one state slot is needed");
     bool same = true;
     for (const auto& g : groups) {
-      if (g.window < 0 || g.chunk < 0) throw PoolError("KvCacheManager: negative window or chunk");
+      if (g.window < 0 || g.chunk < 0 || g.keep_first < 0) throw PoolError("KvCacheManager: negative window, chunk or keep_first");
       pools_.emplace_back(g.num_blocks, g.block_size);
       same = same && g.block_size == groups[0].block_size;
     }
@@ -92,13 +95,14 @@ class KvCacheManager {
     std::vector<std::vector<int>> found;
     const int hits = cached_prefix_pages(tokens, n, &hashes, &found);
     for (size_t g = 0; g < specs_.size(); ++g) {
-      const int lo = first_page_needed(g, hits);
+      const int lo = first_page_needed(g, hits), kept = std::min(hits, specs_[g].kept_pages());
       r.tables[g].assign(hits, -1);
-      for (int i = lo; i < hits; ++i) {
+      for (int i = 0; i < hits; ++i) {
+        if (i >= kept && i < lo) continue;
         pools_[g].retain(found[g][i]);
         r.tables[g][i] = found[g][i];
       }
-      if (specs_[g].limited()) r.released_upto[g] = lo;
+      if (specs_[g].limited()) r.released_upto[g] = std::max(lo, kept);
     }
     r.page_hashes.assign(hashes.begin(), hashes.begin() + hits);
     return hits * specs_[0].block_size;
@@ -160,6 +164,8 @@ class KvCacheManager {
       const int bs = specs_[g].block_size;
       const int first_needed = specs_[g].first_needed(num_computed);  // lowest position still readable
       auto& t = r.tables[g];
+      // the pages of kept first positions are never given back
+      r.released_upto[g] = std::max(r.released_upto[g], std::min(specs_[g].kept_pages(), static_cast<int>(t.size())));
       for (int p = r.released_upto[g]; p < static_cast<int>(t.size()) && (p + 1) * bs <= first_needed; ++p) {
         if (t[p] >= 0) { pools_[g].release(t[p]); t[p] = -1; }
         r.released_upto[g] = p + 1;
@@ -295,7 +301,8 @@ class KvCacheManager {
     for (; hits > 0; --hits) {
       bool ok = true;
       for (size_t g = 0; g < specs_.size() && ok; ++g)
-        for (int i = first_page_needed(g, hits); i < hits && ok; ++i) ok = ids[g][i] >= 0;
+        for (int i = 0; i < hits && ok; ++i)
+          if (i < specs_[g].kept_pages() || i >= first_page_needed(g, hits)) ok = ids[g][i] >= 0;
       if (ok) break;
     }
     if (hashes) *hashes = std::move(hs);

@@ -17,7 +17,10 @@
 // Options that other mixers use: the value plane may have its own head size and fewer heads than the key plane (value
 // head = key head * vkvh / kvh: neighbouring key heads share a value head); `softcap` > 0 bends the scaled score to
 // softcap * tanh(score / softcap); `chunk` > 0 moves lo to the start of the query's block of `chunk` positions (blocks
-// counted from position 0), so a query sees only keys of its own block; the output may be stored as float whatever T.
+// counted from position 0), so a query sees only keys of its own block; the output may be stored as float whatever T;
+// `keep_first` > 0 lets every query also see the keys at positions below it, whatever the window or block (they keep their
+// own positions); `dist_bias` [dist_rows, nh] float adds dist_bias[min(pos - key, dist_rows - 1)][h] to the scaled
+// (and capped) score: a learned bias by distance.
 #include "common.cuh"
 
 namespace vob {
@@ -73,7 +76,8 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
                                const int* __restrict__ token_req, const int* __restrict__ positions,
                                const int* __restrict__ skip_single_cu_q, int nh, int kvh, int hd, int vd, int block_size,
                                int window, float scale, long num_pages, int sink, const T* gate, long gate_stride,
-                               int vkvh, int v_row, float softcap, int chunk, int out_float, int* err) {
+                               int vkvh, int v_row, float softcap, int chunk, int out_float, int keep_first,
+                               const float* __restrict__ dist_bias, int dist_rows, int* err) {
   extern __shared__ float smem[];
   float* qs = smem;                        // [hd]
   float* accs = smem + hd;                 // [ATT_WARPS][vd]
@@ -100,9 +104,13 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
 #pragma unroll
   for (int j = 0; j < ATT_MAXD; ++j) acc[j] = 0.f;
 
-  for (int tile = lo / 32 + ((warp - (lo / 32) % ATT_WARPS + ATT_WARPS) % ATT_WARPS); tile <= pos / 32; tile += ATT_WARPS) {
+  // kept first keys: the tiles that hold them are walked too, the ones between them and the window are passed over
+  const int keep = min(max(keep_first, 0), lo);
+  const int first_tile = keep > 0 ? 0 : lo / 32;
+  for (int tile = first_tile + ((warp - first_tile % ATT_WARPS + ATT_WARPS) % ATT_WARPS); tile <= pos / 32; tile += ATT_WARPS) {
+    if (tile * 32 >= keep && tile * 32 + 31 < lo) continue;
     const int key = tile * 32 + lane;
-    const bool valid = key >= lo && key <= pos;
+    const bool valid = (key >= lo || key < keep) && key <= pos;
     long row = -1;  // element offset of this key's row for kv head kh
     int page = -1;
     if (valid) {
@@ -114,6 +122,7 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
     if (row >= 0) {
       s = dot_row<T>(qs, kcache + row, hd) * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      if (dist_bias) s += dist_bias[(size_t)min(pos - key, dist_rows - 1) * nh + h];
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = (row >= 0) ? expf(s - m_new) : 0.f;
@@ -175,19 +184,20 @@ using namespace vob;
 // has a silent extra entry of score 0 (weights exp(s) / (1 + sum exp(s))); `gate` (rows of gate_stride elements, one
 // number a head): head h of token t is multiplied by sigmoid(gate[t, h]).
 // vkvh, v_row: heads and head size of the value plane [num_pages, vkvh, block_size, v_row] (0: those of the key plane);
-// softcap, chunk: see above (0: off); out_float: out is float whatever `dtype`.
+// softcap, chunk, keep_first, dist_bias: see above (0 / null: off); out_float: out is float whatever `dtype`.
 VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
                                         const int* block_tables, int table_stride, const int* token_req,
                                         const int* positions, const int* skip_single_cu_q, int T, int nh, int kvh, int hd,
                                         int vd, int block_size,
                                         int window, float scale, long num_pages, int sink, const void* gate,
                                         long gate_stride, int vkvh, int v_row, float softcap, int chunk, int out_float,
+                                        int keep_first, const float* dist_bias, int dist_rows,
                                         int dtype, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (vkvh <= 0) vkvh = kvh;
   if (v_row <= 0) v_row = hd;
   if (hd <= 0 || hd > 512 || kvh <= 0 || nh % kvh || block_size <= 0 || vd <= 0 || vd > v_row || vd > 512 || kvh % vkvh ||
-      softcap < 0.f || chunk < 0)
+      softcap < 0.f || chunk < 0 || keep_first < 0 || (dist_bias && dist_rows <= 0))
     return VOB_UNSUPPORTED;
   dim3 grid(T, nh);
   const size_t smem = (size_t)(hd + ATT_WARPS * vd) * sizeof(float);
@@ -195,12 +205,12 @@ VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out,
     return launch_kernel(paged_attention_generic_kernel<float>, grid, ATT_WARPS * 32, smem, stream, (const float*)q, q_stride,
                          (float*)out, (const float*)kcache, (const float*)vcache, block_tables, table_stride, token_req,
                          positions, skip_single_cu_q, nh, kvh, hd, vd, block_size, window, scale, num_pages, sink,
-                         (const float*)gate, gate_stride, vkvh, v_row, softcap, chunk, out_float, err);
+                         (const float*)gate, gate_stride, vkvh, v_row, softcap, chunk, out_float, keep_first, dist_bias, dist_rows, err);
   if (dtype == VOB_BF16)
     return launch_kernel(paged_attention_generic_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream,
                          (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
                          (const __nv_bfloat16*)vcache, block_tables, table_stride, token_req, positions, skip_single_cu_q,
                          nh, kvh, hd, vd, block_size, window, scale, num_pages, sink, (const __nv_bfloat16*)gate,
-                         gate_stride, vkvh, v_row, softcap, chunk, out_float, err);
+                         gate_stride, vkvh, v_row, softcap, chunk, out_float, keep_first, dist_bias, dist_rows, err);
   return VOB_BAD_ARGUMENT;
 }

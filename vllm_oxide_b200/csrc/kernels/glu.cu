@@ -1,0 +1,65 @@
+// A gated feed-forward's activation with clamps, and a bias added to rows.
+//
+//   clamped_glu:  g = min(gate + b_gate, limit);  u = clamp(up + b_up, -limit, limit);  out = g * sigmoid(alpha * g) * (u + 1).
+//                 The input row holds the gate's columns, then the up columns; the biases (float, optional) lie alike.
+//   add_bias:     x[t, :] += b  (float b, x of the model's type).
+//
+// The arithmetic is float; inputs and outputs are of the model's type T.
+#include "common.cuh"
+
+namespace vob {
+
+template <typename T>
+__global__ void clamped_glu_kernel(const T* gu, long gu_stride, const float* __restrict__ bias, T* out, int I, float limit,
+                                   float alpha, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / I, i = idx % I;
+  float g = to_f<T>(gu[t * gu_stride + i]), u = to_f<T>(gu[t * gu_stride + I + i]);
+  if (bias) { g += bias[i]; u += bias[I + i]; }
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  out[idx] = from_f<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+template <typename T>
+__global__ void add_bias_kernel(T* x, const float* __restrict__ bias, int D, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  x[idx] = from_f<T>(to_f<T>(x[idx]) + bias[idx % D]);
+}
+
+}  // namespace vob
+
+using namespace vob;
+
+// gu [T, 2 * I] rows of gu_stride elements; bias float [2 * I] or null; out [T, I] contiguous.
+VOB_API int vob_clamped_glu(const void* gu, long gu_stride, const float* bias, void* out, int T, int I, float limit, float alpha,
+                            int dtype, cudaStream_t stream) {
+  if (T <= 0 || I <= 0) return 0;
+  if (!(limit > 0.f)) return VOB_BAD_ARGUMENT;
+  const size_t total = (size_t)T * I;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == VOB_F32)
+    return launch_kernel(clamped_glu_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, gu_stride, bias, (float*)out, I,
+                         limit, alpha, total);
+  if (dtype == VOB_BF16)
+    return launch_kernel(clamped_glu_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu, gu_stride, bias,
+                         (__nv_bfloat16*)out, I, limit, alpha, total);
+  return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_add_bias(void* x, const float* bias, int T, int D, int dtype, cudaStream_t stream) {
+  if (T <= 0 || D <= 0) return 0;
+  const size_t total = (size_t)T * D;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == VOB_F32)
+    return launch_kernel(add_bias_kernel<float>, grid, dim3(256), 0, stream, (float*)x, bias, D, total);
+  if (dtype == VOB_BF16)
+    return launch_kernel(add_bias_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, bias, D, total);
+  return VOB_BAD_ARGUMENT;
+}

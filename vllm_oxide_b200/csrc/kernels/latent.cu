@@ -10,7 +10,7 @@
 //                  latent's space to the value heads.
 //   latent_query_rotate: the rotated part of every query head, behind its latent part, and zeros up to the row width.
 //
-// The angle of pair i at position p is float(p) * frequency[i], computed where it is used (no table, no position limit);
+// Pairs are neighbours (2i, 2i + 1) or, with `halves`, (i, i + rotary / 2).  The angle of pair i at position p is float(p) * frequency[i], computed where it is used (no table, no position limit);
 // cos and sin are multiplied by an amplitude.  Norms, angles and rotation are float; rows are of the model's type T.
 #include "common.cuh"
 
@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(LP_NT)
 latent_prep_kernel(const T* down, long stride, const float* __restrict__ wq, const float* __restrict__ wkv,
                    const float* __restrict__ freq, float amp, const int* __restrict__ positions, const int* __restrict__ slots,
                    T* cq, T* cache, int q_rank, int kv_rank, int rot, int rotary, int row_width, long num_slots, float eps,
-                   int has_kv, int* err) {
+                   int has_kv, int halves, int* err) {
   __shared__ float scratch[32];
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -60,6 +60,22 @@ latent_prep_kernel(const T* down, long stride, const float* __restrict__ wq, con
   denom = sqrtf(block_sum<LP_NT>(ss, scratch) / (float)kv_rank + eps);
   for (int i = threadIdx.x; i < kv_rank; i += LP_NT) dst[i] = from_f<T>(to_f<T>(kv[i]) / denom * wkv[i]);
   const T* kr = kv + kv_rank;
+  if (halves) {
+    // element i pairs with element i + rotary / 2; what lies behind the rotated elements passes as it is
+    const int half = rotary / 2;
+    for (int i = threadIdx.x; i < rot; i += LP_NT) {
+      float v = to_f<T>(kr[i]);
+      if (i < rotary) {
+        const int p = i < half ? i : i - half;
+        float ra, rb;
+        turn_pair(to_f<T>(kr[p]), to_f<T>(kr[p + half]), __fmul_rn((float)pos, freq[p]), amp, ra, rb);
+        v = i < half ? ra : rb;
+      }
+      dst[kv_rank + i] = from_f<T>(v);
+    }
+    for (int i = kv_rank + rot + threadIdx.x; i < row_width; i += LP_NT) dst[i] = from_f<T>(0.f);
+    return;
+  }
   for (int p = threadIdx.x; p < rot / 2; p += LP_NT) {
     float a = to_f<T>(kr[2 * p]), b = to_f<T>(kr[2 * p + 1]);
     if (2 * p + 1 < rotary) turn_pair(a, b, __fmul_rn((float)pos, freq[p]), amp, a, b);
@@ -74,7 +90,7 @@ latent_prep_kernel(const T* down, long stride, const float* __restrict__ wq, con
 template <typename T>
 __global__ void latent_query_rotate_kernel(const T* q, T* qa, const float* __restrict__ freq, float amp,
                                            const int* __restrict__ positions, int heads, int dk, int rot, int rotary, int offset,
-                                           int row_width) {
+                                           int row_width, int halves) {
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int pos = positions[t];
@@ -86,7 +102,12 @@ __global__ void latent_query_rotate_kernel(const T* q, T* qa, const float* __res
     if (i < rot) {
       const T* src = q + ((size_t)t * heads + h) * (dk + rot) + dk;
       v = to_f<T>(src[i]);
-      if ((i | 1) < rotary) {
+      if (halves && i < rotary) {
+        const int half = rotary / 2, p = i < half ? i : i - half;
+        float ra, rb;
+        turn_pair(to_f<T>(src[p]), to_f<T>(src[p + half]), __fmul_rn((float)pos, freq[p]), amp, ra, rb);
+        v = i < half ? ra : rb;
+      } else if (!halves && (i | 1) < rotary) {
         float a = to_f<T>(src[i & ~1]), b = to_f<T>(src[i | 1]), ra, rb;
         turn_pair(a, b, __fmul_rn((float)pos, freq[i >> 1]), amp, ra, rb);
         v = (i & 1) ? rb : ra;
@@ -142,15 +163,42 @@ head_linear_kernel(const T* x, long x_ts, long x_hs, const T* __restrict__ w, T*
   }
 }
 
+// x[t, i] *= sigmoid(gate[t, i]) for the first `width` elements of every row (rows of x_stride / gate_stride elements).
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(T* x, long x_stride, const T* gate, long gate_stride, int width, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / width, i = idx % width;
+  const float g = to_f<T>(gate[t * gate_stride + i]);
+  T* px = x + t * x_stride + i;
+  *px = from_f<T>(to_f<T>(*px) / (1.f + expf(-g)));
+}
+
 }  // namespace vob
 
 using namespace vob;
+
+VOB_API int vob_sigmoid_gate_mul(void* x, long x_stride, const void* gate, long gate_stride, int T, int width, int dtype,
+                                 cudaStream_t stream) {
+  if (T <= 0 || width <= 0) return 0;
+  const size_t total = (size_t)T * width;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == VOB_F32)
+    return launch_kernel(sigmoid_gate_mul_kernel<float>, grid, dim3(256), 0, stream, (float*)x, x_stride, (const float*)gate,
+                         gate_stride, width, total);
+  if (dtype == VOB_BF16)
+    return launch_kernel(sigmoid_gate_mul_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, x_stride,
+                         (const __nv_bfloat16*)gate, gate_stride, width, total);
+  return VOB_BAD_ARGUMENT;
+}
 
 // down [T, >= q_rank (+ kv_rank + rot)] rows of `stride` elements; wq [q_rank], wkv [kv_rank], freq [rotary/2] float;
 // cq [T, q_rank]; cache: rows of row_width elements, one per slot; slots [T] (-1: skip).
 VOB_API int vob_latent_prep(const void* down, long stride, const float* wq, const float* wkv, const float* freq, float amp,
                             const int* positions, const int* slots, void* cq, void* cache, int T, int q_rank, int kv_rank, int rot,
-                            int rotary, int row_width, long num_slots, float eps, int has_kv, int dtype, int* err,
+                            int rotary, int row_width, long num_slots, float eps, int has_kv, int halves, int dtype, int* err,
                             cudaStream_t stream) {
   if (T <= 0) return 0;
   if (q_rank <= 0 || (has_kv && (kv_rank <= 0 || rot < 0 || rotary > rot || (rotary & 1) || row_width < kv_rank + rot)))
@@ -158,25 +206,26 @@ VOB_API int vob_latent_prep(const void* down, long stride, const float* wq, cons
   if (dtype == VOB_F32)
     return launch_kernel(latent_prep_kernel<float>, dim3(T), dim3(LP_NT), 0, stream, (const float*)down, stride, wq, wkv, freq, amp,
                          positions, slots, (float*)cq, (float*)cache, q_rank, kv_rank, rot, rotary, row_width, num_slots, eps, has_kv,
-                         err);
+                         halves, err);
   if (dtype == VOB_BF16)
     return launch_kernel(latent_prep_kernel<__nv_bfloat16>, dim3(T), dim3(LP_NT), 0, stream, (const __nv_bfloat16*)down, stride, wq,
                          wkv, freq, amp, positions, slots, (__nv_bfloat16*)cq, (__nv_bfloat16*)cache, q_rank, kv_rank, rot, rotary,
-                         row_width, num_slots, eps, has_kv, err);
+                         row_width, num_slots, eps, has_kv, halves, err);
   return VOB_BAD_ARGUMENT;
 }
 
 VOB_API int vob_latent_query_rotate(const void* q, void* qa, const float* freq, float amp, const int* positions, int T, int heads,
-                                    int dk, int rot, int rotary, int offset, int row_width, int dtype, cudaStream_t stream) {
+                                    int dk, int rot, int rotary, int offset, int row_width, int halves, int dtype,
+                                    cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rotary > rot || (rotary & 1) || offset + rot > row_width) return VOB_BAD_ARGUMENT;
   if (row_width == offset) return 0;
   if (dtype == VOB_F32)
     return launch_kernel(latent_query_rotate_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)q, (float*)qa, freq, amp,
-                         positions, heads, dk, rot, rotary, offset, row_width);
+                         positions, heads, dk, rot, rotary, offset, row_width, halves);
   if (dtype == VOB_BF16)
     return launch_kernel(latent_query_rotate_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)q,
-                         (__nv_bfloat16*)qa, freq, amp, positions, heads, dk, rot, rotary, offset, row_width);
+                         (__nv_bfloat16*)qa, freq, amp, positions, heads, dk, rot, rotary, offset, row_width, halves);
   return VOB_BAD_ARGUMENT;
 }
 

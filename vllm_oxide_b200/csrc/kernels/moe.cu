@@ -22,6 +22,16 @@ namespace vob {
 
 constexpr int MOE_TM = 64;       // rows of a product tile; experts' row ranges are padded to it
 
+// What a (gate, up) pair of features becomes: SiLU(gate) * up, or with a clamp (`limit` > 0)
+// g = min(gate, limit), u = clamp(up, -limit, limit): g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float gated_pair(float gate, float up, float limit) {
+  if (limit > 0.f) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+  }
+  return gate / (1.f + expf(-gate)) * up;
+}
+
 // ---------------------------------------------------------------- routing
 struct Best { float v; int i; };
 __device__ __forceinline__ Best better(Best a, Best b) { return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a; }
@@ -42,7 +52,8 @@ constexpr int ROUTE_TOKENS = 4;   // tokens a block: the router's rows are read 
 
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_NT)
-moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __restrict__ correction, int* ids, float* weights,
+moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __restrict__ router_bias,
+                 const float* __restrict__ correction, int* ids, float* weights,
                  int W, int E, int top, int count, int keep, int sigmoid_scores, int group_top, int normalise, float weight_scale,
                  int num_tokens, int per_block) {
   extern __shared__ __align__(16) float route_smem[];
@@ -90,7 +101,7 @@ moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __
 #pragma unroll
     for (int k = 0; k < ROUTE_TOKENS; ++k) {
       const float sum = warp_sum(z[k]);
-      if (lane == 0 && k < here) lists[(size_t)k * (2 * E + count) + e] = sum;
+      if (lane == 0 && k < here) lists[(size_t)k * (2 * E + count) + e] = router_bias ? sum + router_bias[e] : sum;
     }
   }
   __syncthreads();
@@ -209,12 +220,12 @@ moe_align_kernel(const int* ids, int* slot_of, int* row_token, int* tile_expert,
 // ---------------------------------------------------------------- the experts' products
 constexpr int MG_N = 64, MG_K = 16;
 
-// EPI 0: as it is; 1: squared relu; 2: SiLU(even column) * odd column into column / 2.  GATHER: row r of A is
+// EPI 0: as it is; 1: squared relu; 2: gated_pair(even column, odd column) into column / 2.  GATHER: row r of A is
 // a[row_token[r]], else a[r].
 template <typename TA, typename TC, int EPI, bool GATHER>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* A, long lda, const TA* __restrict__ W, TC* C, long ldc, const int* row_token,
-                const int* tile_expert, int N, int K) {
+                const int* tile_expert, int N, int K, float glu_limit) {
   __shared__ float As[MG_K][MOE_TM + 4];
   __shared__ float Ws[MG_K][MG_N + 4];
   __shared__ int src[MOE_TM];
@@ -271,7 +282,7 @@ moe_gemm_kernel(const TA* A, long lda, const TA* __restrict__ W, TC* C, long ldc
         const int n = n0 + tx * 4 + j;
         if (n + 1 >= N) continue;
         const float g = acc[i][j];
-        C[(size_t)m * ldc + n / 2] = from_f<TC>(g / (1.f + expf(-g)) * acc[i][j + 1]);
+        C[(size_t)m * ldc + n / 2] = from_f<TC>(gated_pair(g, acc[i][j + 1], glu_limit));
       }
       continue;
     }
@@ -342,7 +353,7 @@ constexpr int MV_ROWS = 64;       // output features a block
 template <int EPI, bool BY_TOKEN>
 __global__ void __launch_bounds__(256)
 moe_gemv_kernel(const __nv_bfloat16* A, long lda, const __nv_bfloat16* __restrict__ W, void* C, long ldc, const int* ids,
-                const int* order, int top, int N, int K) {
+                const int* order, int top, int N, int K, float glu_limit) {
   extern __shared__ uint4 gemv_smem[];     // the input row: K bfloat16
   pdl_launch_dependents();
   pdl_wait();
@@ -389,7 +400,7 @@ moe_gemv_kernel(const __nv_bfloat16* A, long lda, const __nv_bfloat16* __restric
       for (int r = 0; r < 4; r += 2) {
         const int n = n0 + rg * 4 + r;
         if (lane == 0 && n + 1 < N)
-          reinterpret_cast<__nv_bfloat16*>(C)[(size_t)pair * ldc + n / 2] = __float2bfloat16_rn(v[r] / (1.f + expf(-v[r])) * v[r + 1]);
+          reinterpret_cast<__nv_bfloat16*>(C)[(size_t)pair * ldc + n / 2] = __float2bfloat16_rn(gated_pair(v[r], v[r + 1], glu_limit));
       }
       continue;
     }
@@ -444,7 +455,8 @@ VOB_API int vob_moe_row_tile() { return MOE_TM; }
 
 // correction may be null; sigmoid_scores: scores are sigmoid(z), not the softmax; group_top 2: a group counts by its two best;
 // normalise: the chosen scores are divided by their sum; weight_scale: a factor on the weights.
-VOB_API int vob_moe_route(const void* h, const float* w_router, const float* correction, int* ids, float* weights, int T, int W,
+VOB_API int vob_moe_route(const void* h, const float* w_router, const float* router_bias, const float* correction, int* ids,
+                          float* weights, int T, int W,
                           int E, int top, int count, int keep, int sigmoid_scores, int group_top, int normalise,
                           float weight_scale, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
@@ -461,7 +473,7 @@ VOB_API int vob_moe_route(const void* h, const float* w_router, const float* cor
     if (smem > 48 * 1024)                                                                                                \
       cudaFuncSetAttribute(moe_route_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
     return launch_kernel(moe_route_kernel<TYPE>, dim3((T + per_block - 1) / per_block), ROUTE_NT, smem, stream,          \
-                         (const TYPE*)h, w_router, correction, ids, weights, W, E, top, count, keep, sigmoid_scores,     \
+                         (const TYPE*)h, w_router, router_bias, correction, ids, weights, W, E, top, count, keep, sigmoid_scores,     \
                          group_top, normalise, weight_scale, T, per_block);                                              \
   } while (0)
   if (dtype == VOB_F32) VOB_ROUTE(float);
@@ -482,14 +494,15 @@ VOB_API int vob_moe_align(const int* ids, int* slot_of, int* row_token, int* til
 // with `c_float`.  epilogue 0: as it is, 1: squared relu, 2: SiLU(gate) * up over rows of W in (gate, up) pairs: C has N / 2
 // columns.
 VOB_API int vob_moe_gemm(const void* A, long lda, const void* W, void* C, long ldc, const int* row_token, const int* tile_expert,
-                         int max_rows, int N, int K, int epilogue, int gather, int c_float, int dtype, cudaStream_t stream) {
+                         int max_rows, int N, int K, int epilogue, int gather, int c_float, float glu_limit, int dtype,
+                         cudaStream_t stream) {
   if (max_rows <= 0 || N <= 0) return 0;
   if (K <= 0 || max_rows % MOE_TM) return VOB_BAD_ARGUMENT;
   dim3 grid((N + MG_N - 1) / MG_N, max_rows / MOE_TM);
   if (grid.y > 65535) return VOB_UNSUPPORTED;
 #define VOB_MG(TA, TC, EPI, G)                                                                                       \
   return launch_kernel(moe_gemm_kernel<TA, TC, EPI, G>, grid, 256, 0, stream, (const TA*)A, lda, (const TA*)W, (TC*)C, ldc, \
-                       row_token, tile_expert, N, K)
+                       row_token, tile_expert, N, K, glu_limit)
 #define VOB_MG_TYPE(TA)                                                   \
   if (epilogue == 1 && gather && !c_float) VOB_MG(TA, TA, 1, true);       \
   if (epilogue == 2 && gather && !c_float) VOB_MG(TA, TA, 2, true);       \
@@ -512,7 +525,7 @@ VOB_API int vob_moe_order(const int* ids, int* order, int n, int E, cudaStream_t
 // C [pairs, ldc]: bfloat16 with the squared relu (`epilogue` 1) or with SiLU(gate) * up over rows of W in (gate, up) pairs
 // (2: N / 2 columns), or float (0).  order: the pairs by expert (vob_moe_order).
 VOB_API int vob_moe_gemv(const void* A, long lda, const void* W, void* C, long ldc, const int* ids, const int* order, int n,
-                         int top, int N, int K, int epilogue, int by_token, cudaStream_t stream) {
+                         int top, int N, int K, int epilogue, int by_token, float glu_limit, cudaStream_t stream) {
   if (n <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || (lda * 2) % 16 || ((uintptr_t)A | (uintptr_t)W) % 16 || n > 65535) return VOB_UNSUPPORTED;
   const size_t smem = (size_t)K * 2;
@@ -522,7 +535,7 @@ VOB_API int vob_moe_gemv(const void* A, long lda, const void* W, void* C, long l
   do {                                                                                                                      \
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_gemv_kernel<EPI, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     return launch_kernel(moe_gemv_kernel<EPI, BT>, grid, 256, smem, stream, (const __nv_bfloat16*)A, lda,                   \
-                         (const __nv_bfloat16*)W, C, ldc, ids, order, top, N, K);                                          \
+                         (const __nv_bfloat16*)W, C, ldc, ids, order, top, N, K, glu_limit);                                       \
   } while (0)
   if (epilogue == 1 && by_token) VOB_MV(1, true);
   if (epilogue == 2 && by_token && N % 2 == 0) VOB_MV(2, true);

@@ -40,7 +40,7 @@ enum { MT_EPI_RELU2_BF16 = 0, MT_EPI_F32 = 1, MT_EPI_SILU_PAIRS_BF16 = 2 };
 template <int EPI>
 __global__ void __launch_bounds__(MT_THREADS, 1)
 moe_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, void* out, long ldo,
-               const int* row_token, const int* tile_expert, int row_tiles, int N, int K, int* err) {
+               const int* row_token, const int* tile_expert, int row_tiles, int N, int K, float glu_limit, int* err) {
   constexpr int S = MT_S, A_BYTES = MT_ROWS * 128, STAGE_BYTES = MT_STAGE_BYTES;
   constexpr int TMEM_COLS = 2 * MT_NT;
   extern __shared__ __align__(1024) char smem_raw[];
@@ -165,7 +165,10 @@ moe_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if ((odd ? live1 : live0) && (n | 1) < N) {
               const long m = (long)mt * MT_NT + c0 + j + (odd ? 1 : 0);
               reinterpret_cast<__nv_bfloat16*>(out)[m * ldo + (n >> 1)] =
-                  __float2bfloat16_rn(__fdividef(gate, 1.f + __expf(-gate)) * up);
+                  __float2bfloat16_rn(glu_limit > 0.f
+                                          ? __fdividef(fminf(gate, glu_limit), 1.f + __expf(-1.702f * fminf(gate, glu_limit))) *
+                                                (fminf(fmaxf(up, -glu_limit), glu_limit) + 1.f)
+                                          : __fdividef(gate, 1.f + __expf(-gate)) * up);
             }
           }
           continue;
@@ -220,9 +223,11 @@ VOB_API int vob_moe_tc5_row_tile() { return MT_NT; }
 
 // map_w: tensor map of W [experts * N, K] with box 128 rows; map_x: tensor map of the sorted rows [max_rows, K] with box 128
 // rows (vob_tensor_map_bf16_2d).  out [max_rows, ldo]: bfloat16 with the squared relu (epilogue 0), float (1), or bfloat16
-// SiLU(gate) * up over rows of W in (gate, up) pairs (2: N / 2 columns).
+// SiLU(gate) * up over rows of W in (gate, up) pairs (2: N / 2 columns; with glu_limit > 0 the clamped form
+// min(gate, limit) * sigmoid(1.702 min(gate, limit)) * (clamp(up, -limit, limit) + 1)).
 VOB_API int vob_moe_gemm_tc5(const void* map_w, const void* map_x, void* out, long ldo, const int* row_token,
-                             const int* tile_expert, int max_rows, int N, int K, int epilogue, int* err, cudaStream_t stream) {
+                             const int* tile_expert, int max_rows, int N, int K, int epilogue, float glu_limit, int* err,
+                             cudaStream_t stream) {
   if (max_rows <= 0 || N <= 0) return 0;
   if (!map_w || !map_x || K <= 0 || K % 8 || max_rows % MT_NT) return VOB_BAD_ARGUMENT;
   const int row_tiles = max_rows / MT_NT;
@@ -237,7 +242,7 @@ VOB_API int vob_moe_gemm_tc5(const void* map_w, const void* map_x, void* out, lo
       configured[EPI] = true;                                                                                              \
     }                                                                                                                      \
     return launch_kernel(moe_tc5_kernel<EPI>, dim3(blocks), MT_THREADS, MT_SMEM, stream, *(const CUtensorMap*)map_w,       \
-                         *(const CUtensorMap*)map_x, out, ldo, row_token, tile_expert, row_tiles, N, K, err);              \
+                         *(const CUtensorMap*)map_x, out, ldo, row_token, tile_expert, row_tiles, N, K, glu_limit, err);          \
   } while (0)
   if (epilogue == MT_EPI_RELU2_BF16) VOB_MT(MT_EPI_RELU2_BF16);
   if (epilogue == MT_EPI_F32) VOB_MT(MT_EPI_F32);

@@ -124,6 +124,84 @@ layer_norm_step_kernel(float* stream, const T* y1, const T* y2, const float* __r
   }
 }
 
+
+// The same pass with an RMS norm instead: x = y1 * open_scale (`init`: the row begins here with the embedded token) or
+// x = stream[token] + mult * (y1 + y2); the row is stored; out = x / sqrt(mean(x^2) + eps) * (gain_offset + w)
+// (gain_offset 1: a gain stored around zero; 0: a plain gain).  Float throughout; y1, y2, out of the model's type T.
+template <typename T>
+__global__ void __launch_bounds__(PN_NT)
+rms_norm_step_kernel(float* stream, const T* y1, const T* y2, const float* __restrict__ w, T* out, const int* __restrict__ rows,
+                     int num_src_rows, int D, float eps, int init, float mult, float open_scale, float gain_offset, int* err,
+                     int wide) {
+  extern __shared__ __align__(16) float pn_row[];    // [D] the new row
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  int src = r;
+  if (rows) {
+    src = rows[r];
+    if (src < 0 || src >= num_src_rows) {
+      if (threadIdx.x == 0) atomicOr(err, VOB_ERR_ROW);
+      return;
+    }
+  }
+  const size_t base = (size_t)src * D;
+  const bool store = rows == nullptr && (init || y1 || y2);
+  float sq = 0.f;
+  const int step = wide ? 4 : 1;
+  for (int d = threadIdx.x * step; d < D; d += PN_NT * step) {
+    float x[4] = {0.f, 0.f, 0.f, 0.f}, a[4] = {0.f, 0.f, 0.f, 0.f}, c[4] = {0.f, 0.f, 0.f, 0.f};
+    if (wide) {
+      if (!init) load4(stream + base + d, x);
+      if (y1) load4(y1 + base + d, a);
+      if (y2) load4(y2 + base + d, c);
+    } else {
+      if (!init) x[0] = stream[base + d];
+      if (y1) a[0] = to_f<T>(y1[base + d]);
+      if (y2) c[0] = to_f<T>(y2[base + d]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i >= step) break;
+      if (init) x[i] = __fmul_rn(a[i], open_scale);
+      else if (y1 || y2) x[i] = __fadd_rn(x[i], __fmul_rn(mult, __fadd_rn(a[i], c[i])));
+      sq = fmaf(x[i], x[i], sq);
+      pn_row[d + i] = x[i];
+    }
+    if (store) {
+      if (wide) store4(stream + base + d, x);
+      else stream[base + d] = x[0];
+    }
+  }
+  if (!out) return;
+  const float inv = 1.f / sqrtf(block_sum<PN_NT>(sq, scratch) / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += PN_NT)
+    out[(size_t)r * D + d] = from_f<T>(pn_row[d] * inv * (gain_offset + w[d]));
+}
+
+// out = 0.5 * (a / rms(a) * wa + b / rms(b) * wb): two mixers side by side over the same input, each with an RMS norm over
+// the width (plain gains), then their mean.  One block a token; float sums.
+template <typename T>
+__global__ void __launch_bounds__(PN_NT)
+pair_norm_mean_kernel(const T* a, const T* b, const float* __restrict__ wa, const float* __restrict__ wb, T* out, int D,
+                      float eps) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * D;
+  float sa = 0.f, sb = 0.f;
+  for (int d = threadIdx.x; d < D; d += PN_NT) {
+    const float x = to_f<T>(a[base + d]), y = to_f<T>(b[base + d]);
+    sa = fmaf(x, x, sa);
+    sb = fmaf(y, y, sb);
+  }
+  const float ia = 1.f / sqrtf(block_sum<PN_NT>(sa, scratch) / (float)D + eps);
+  const float ib = 1.f / sqrtf(block_sum<PN_NT>(sb, scratch) / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += PN_NT)
+    out[base + d] = from_f<T>(0.5f * (to_f<T>(a[base + d]) * ia * wa[d] + to_f<T>(b[base + d]) * ib * wb[d]));
+}
+
 }  // namespace vob
 
 using namespace vob;
@@ -148,5 +226,40 @@ VOB_API int vob_layer_norm_step(float* stream, const void* y1, const void* y2, c
   if (dtype == VOB_F32) VOB_PN_LAUNCH(float);
   if (dtype == VOB_BF16) VOB_PN_LAUNCH(__nv_bfloat16);
 #undef VOB_PN_LAUNCH
+  return VOB_BAD_ARGUMENT;
+}
+
+// As vob_layer_norm_step with an RMS norm: see rms_norm_step_kernel.  w [D] float; b is not taken.
+VOB_API int vob_rms_norm_step(float* stream, const void* y1, const void* y2, const float* w, void* out, const int* rows, int n_out,
+                              int num_src_rows, int D, float eps, int init, float mult, float open_scale, float gain_offset,
+                              int dtype, int* err, cudaStream_t stream_) {
+  if (n_out <= 0) return 0;
+  if (D <= 0 || (rows && !out) || (out && !w) || (init && !y1)) return VOB_BAD_ARGUMENT;
+  const size_t smem = (size_t)D * sizeof(float);
+  if (smem > 200 * 1024) return VOB_UNSUPPORTED;
+  const int wide = D % 4 == 0 && (((uintptr_t)stream | (uintptr_t)y1 | (uintptr_t)y2) & 15) == 0;
+#define VOB_RN_LAUNCH(TYPE)                                                                                             \
+  do {                                                                                                                  \
+    if (smem > 48 * 1024)                                                                                               \
+      cudaFuncSetAttribute(rms_norm_step_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+    return launch_kernel(rms_norm_step_kernel<TYPE>, dim3(n_out), PN_NT, smem, stream_, stream, (const TYPE*)y1,        \
+                         (const TYPE*)y2, w, (TYPE*)out, rows, num_src_rows, D, eps, init, mult, open_scale, gain_offset, \
+                         err, wide);                                                                                    \
+  } while (0)
+  if (dtype == VOB_F32) VOB_RN_LAUNCH(float);
+  if (dtype == VOB_BF16) VOB_RN_LAUNCH(__nv_bfloat16);
+#undef VOB_RN_LAUNCH
+  return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_pair_norm_mean(const void* a, const void* b, const float* wa, const float* wb, void* out, int T, int D, float eps,
+                               int dtype, cudaStream_t stream) {
+  if (T <= 0 || D <= 0) return 0;
+  if (dtype == VOB_F32)
+    return launch_kernel(pair_norm_mean_kernel<float>, dim3(T), PN_NT, 0, stream, (const float*)a, (const float*)b, wa, wb,
+                         (float*)out, D, eps);
+  if (dtype == VOB_BF16)
+    return launch_kernel(pair_norm_mean_kernel<__nv_bfloat16>, dim3(T), PN_NT, 0, stream, (const __nv_bfloat16*)a,
+                         (const __nv_bfloat16*)b, wa, wb, (__nv_bfloat16*)out, D, eps);
   return VOB_BAD_ARGUMENT;
 }

@@ -204,7 +204,8 @@ def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, rule, kcache, vca
 
 def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, token_req, positions, num_tokens, nh, kvh,
                             hd, window: int, scale: float, err, skip_single_cu_q=None, value_dim: Optional[int] = None,
-                            sink: bool = False, gate=None, gate_stride: int = 0, softcap: float = 0.0, chunk: int = 0) -> None:
+                            sink: bool = False, gate=None, gate_stride: int = 0, softcap: float = 0.0, chunk: int = 0,
+                            keep_first: int = 0, dist_bias=None) -> None:
     """Every token of the batch; with `skip_single_cu_q` (the batch's cu_q) the tokens of requests that
     bring exactly one token are left to the decode kernel.  `value_dim`: only that many leading elements of a value
     row are read and `out` is [tokens, nh * value_dim] (keys and values may then be one and the same plane).
@@ -213,8 +214,11 @@ def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, toke
     [pages, value heads, page size, value size] of another shape than the key plane is read by its own shape (neighbouring
     key heads share a value head) and `out` is [tokens, nh * value size]; `softcap` > 0: scores become softcap *
     tanh(score / softcap); `chunk` > 0: a query sees only keys of its own block of `chunk` positions; a float32 `out`
-    beside bfloat16 inputs is stored unrounded."""
-    _cuda(q, out, kcache, vcache, block_tables, token_req, positions, gate)
+    beside bfloat16 inputs is stored unrounded.  `keep_first` > 0: the keys at positions below it are seen by every later
+    query, whatever the window; `dist_bias` (float [rows, nh]): dist_bias[min(query position - key position, rows - 1), h]
+    is added to head h's scaled score."""
+    _cuda(q, out, kcache, vcache, block_tables, token_req, positions, gate, dist_bias)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[1] == nh)
     assert gate is None or gate.dtype == q.dtype
     own_shape = vcache.shape[1] != kcache.shape[1] or vcache.shape[3] != kcache.shape[3]
     if own_shape:
@@ -228,7 +232,8 @@ def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, toke
                                              hd if value_dim is None else int(value_dim), kcache.shape[2], window,
                                              ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), int(bool(sink)), _p(gate),
                                              ctypes.c_long(gate_stride), vcache.shape[1], vcache.shape[3],
-                                             ctypes.c_float(softcap), int(chunk), int(out.dtype != q.dtype), _code(q.dtype),
+                                             ctypes.c_float(softcap), int(chunk), int(out.dtype != q.dtype), int(keep_first),
+                                             _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _code(q.dtype),
                                              _p(err), _stream()),
            "paged_attention_generic")
 
@@ -292,6 +297,78 @@ def layer_norm_step(stream, eps: float, err, y1=None, y2=None, w=None, b=None, o
            "layer_norm_step")
 
 
+def sigmoid_gate_mul(x, gate, width: int) -> None:
+    """x[t, i] *= sigmoid(gate[t, i]) for i < width; x and gate may be columns of wider rows."""
+    _cuda(x, gate)
+    assert x.dtype == gate.dtype and x.stride(1) == 1 and gate.stride(1) == 1 and x.shape[0] == gate.shape[0]
+    _check(lib().vob_sigmoid_gate_mul(_p(x), ctypes.c_long(x.stride(0)), _p(gate), ctypes.c_long(gate.stride(0)), x.shape[0], width,
+                                      _code(x.dtype), _stream()), "sigmoid_gate_mul")
+
+
+def rms_norm_step(stream, eps: float, err, y1=None, y2=None, w=None, out=None, rows=None, n_out: Optional[int] = None,
+                  init: bool = False, mult: float = 1.0, open_scale: float = 1.0, gain_offset: float = 0.0) -> None:
+    """One pass over a float residual stream [tokens, width] around layers whose sublayers share one RMS norm: x = y1 *
+    open_scale (`init`: the stream begins with the embedded tokens) or x = the stream's row + mult * (y1 + y2); the row is
+    stored; out = x / sqrt(mean(x^2) + eps) * (gain_offset + w).  With `rows` (source rows, `n_out` of them) only `out` is
+    computed and nothing is stored."""
+    _cuda(stream, y1, y2, w, out, rows)
+    assert stream.dtype == torch.float32 and stream.is_contiguous()
+    assert w is None or (w.dtype == torch.float32 and w.is_contiguous())
+    act = next((t for t in (out, y1, y2) if t is not None), None)
+    for t in (y1, y2, out):
+        assert t is None or (t.dtype == act.dtype and t.is_contiguous() and t.shape[1] == stream.shape[1])
+    n_src = stream.shape[0]
+    n = n_src if rows is None else int(n_out)
+    _check(lib().vob_rms_norm_step(_p(stream), _p(y1), _p(y2), _p(w), _p(out), _p(rows), n, n_src, stream.shape[1],
+                                   ctypes.c_float(eps), int(bool(init)), ctypes.c_float(mult), ctypes.c_float(open_scale),
+                                   ctypes.c_float(gain_offset), _code(act.dtype if act is not None else torch.float32), _p(err),
+                                   _stream()), "rms_norm_step")
+
+
+def pair_norm_mean(a, b, wa, wb, out, eps: float) -> None:
+    """out = (a / rms(a) * wa + b / rms(b) * wb) / 2, row by row (float sums; a, b, out of one type, wa and wb float)."""
+    _cuda(a, b, wa, wb, out)
+    assert a.dtype == b.dtype == out.dtype and a.is_contiguous() and b.is_contiguous() and out.is_contiguous()
+    assert a.shape == b.shape == out.shape and wa.dtype == wb.dtype == torch.float32
+    _check(lib().vob_pair_norm_mean(_p(a), _p(b), _p(wa), _p(wb), _p(out), a.shape[0], a.shape[1], ctypes.c_float(eps),
+                                    _code(a.dtype), _stream()), "pair_norm_mean")
+
+
+def unit_qk_kv_write(x, slots, q_out, kcache, vcache, num_tokens: int, nh: int, kvh: int, dim: int, vdim: int, eps: float,
+                     unit: bool, write_kv: bool, err) -> None:
+    """x float [tokens, (nh + kvh) * dim + kvh * vdim] (q heads, k heads, v heads) -> q_out [tokens, nh * kd_row] of the
+    model's type, k and v into the token's slot of kcache [pages, kvh, page, kd_row] and vcache [pages, kvh, page, vd_row];
+    `unit`: every q and k head is divided by its root mean square over `dim` first (no gain).  Heads wider than dim / vdim
+    in the planes get zeros behind."""
+    _cuda(x, slots, q_out, kcache, vcache)
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == (nh + kvh) * dim + kvh * vdim
+    assert q_out.is_contiguous() and kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == vcache.dtype == q_out.dtype
+    kd_row, vd_row = kcache.shape[3], vcache.shape[3]
+    assert q_out.shape[1] == nh * kd_row and kcache.shape[1] == vcache.shape[1] == kvh
+    _check(lib().vob_unit_qk_kv_write(_p(x), _p(slots), _p(q_out), _p(kcache), _p(vcache), num_tokens, nh, kvh, dim, vdim, kd_row,
+                                      vd_row, kcache.shape[2], ctypes.c_long(kcache.shape[0] * kcache.shape[2]),
+                                      ctypes.c_float(eps), int(bool(unit)), int(bool(write_kv)), _code(q_out.dtype), _p(err),
+                                      _stream()), "unit_qk_kv_write")
+
+
+def clamped_glu(gate_up, bias, out, limit: float, alpha: float = 1.702) -> None:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate + b, limit), u = clamp(up + b, -limit, limit); gate_up
+    [tokens, 2 * I]: the gate's columns, then the up columns; bias float [2 * I] or None."""
+    _cuda(gate_up, bias, out)
+    I = out.shape[1]
+    assert gate_up.stride(1) == 1 and gate_up.shape[1] == 2 * I and out.is_contiguous() and gate_up.dtype == out.dtype
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * I and bias.is_contiguous())
+    _check(lib().vob_clamped_glu(_p(gate_up), ctypes.c_long(gate_up.stride(0)), _p(bias), _p(out), out.shape[0], I,
+                                 ctypes.c_float(limit), ctypes.c_float(alpha), _code(out.dtype), _stream()), "clamped_glu")
+
+
+def add_bias(x, bias) -> None:
+    """x[t, :] += bias (float bias, in place)."""
+    _cuda(x, bias)
+    assert x.is_contiguous() and bias.dtype == torch.float32 and bias.numel() == x.shape[1]
+    _check(lib().vob_add_bias(_p(x), _p(bias), x.shape[0], x.shape[1], _code(x.dtype), _stream()), "add_bias")
+
+
 def rope_shared_kv_write(qk, positions, slots, rule, kcache, vcache, num_tokens: int, nh: int, kvh: int, hd: int,
                          write_kv: bool, err) -> None:
     """A merged q|k row of an attention whose values are its keys: query heads rotated in place, every key head written
@@ -328,17 +405,19 @@ def residual_norm_step(stream, eps: float, err, y=None, w_post=None, inject=None
            "residual_norm_step")
 
 
-def short_conv_silu(x, channels: int, taps_w, state, conv_off: int, token_req, cu_q, state_slots, out, num_tokens: int, err) -> None:
+def short_conv_silu(x, channels: int, taps_w, state, conv_off: int, token_req, cu_q, state_slots, out, num_tokens: int, err,
+                    activation: bool = True) -> None:
     """out[t, c] = SiLU(sum_j taps_w[c, j] * x[t - (taps - 1) + j, c]) over every request's tokens of this step (float out
     [tokens, channels]); the inputs before a portion's start come from the request's slot: state [slots, n] float, the
-    last taps - 1 inputs of every channel at conv_off.  x: the first `channels` columns of its rows."""
+    last taps - 1 inputs of every channel at conv_off.  x: the first `channels` columns of its rows.  `activation` False:
+    the filter's output as it is.  `state` may be columns of a wider tensor."""
     _cuda(x, taps_w, state, token_req, cu_q, state_slots, out)
     assert x.stride(1) == 1 and taps_w.dtype == torch.float32 and taps_w.is_contiguous() and taps_w.shape[0] == channels
-    assert state.dtype == torch.float32 and state.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous()
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and out.dtype == torch.float32 and out.is_contiguous()
     _check(lib().vob_short_conv_silu(_p(x), ctypes.c_long(x.stride(0)), _p(taps_w), _p(state), ctypes.c_long(state.stride(0)),
                                      ctypes.c_long(conv_off), _p(token_req), _p(cu_q), _p(state_slots), _p(out), num_tokens,
-                                     channels, taps_w.shape[1], ctypes.c_long(state.shape[0]), _code(x.dtype), _p(err),
-                                     _stream()), "short_conv_silu")
+                                     channels, taps_w.shape[1], ctypes.c_long(state.shape[0]), int(bool(activation)),
+                                     _code(x.dtype), _p(err), _stream()), "short_conv_silu")
 
 
 def short_conv_state(x, channels: int, taps: int, state, conv_off: int, cu_q, state_slots, num_requests: int) -> None:
@@ -350,40 +429,45 @@ def short_conv_state(x, channels: int, taps: int, state, conv_off: int, cu_q, st
                                       ctypes.c_long(state.shape[0]), _code(x.dtype), _stream()), "short_conv_state")
 
 
-def short_conv_step(x, channels: int, taps_w, state, conv_off: int, cu_q, state_slots, out, num_requests: int, err) -> None:
+def short_conv_step(x, channels: int, taps_w, state, conv_off: int, cu_q, state_slots, out, num_requests: int, err,
+                    activation: bool = True) -> None:
     """short_conv_silu and short_conv_state in one launch, a thread a (request, channel): for steps whose portions are
     short (decoding).  Same numbers."""
     _cuda(x, taps_w, state, cu_q, state_slots, out)
     assert x.stride(1) == 1 and taps_w.dtype == torch.float32 and taps_w.is_contiguous() and taps_w.shape[0] == channels
-    assert state.dtype == torch.float32 and state.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous()
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and out.dtype == torch.float32 and out.is_contiguous()
     _check(lib().vob_short_conv_step(_p(x), ctypes.c_long(x.stride(0)), _p(taps_w), _p(state), ctypes.c_long(state.stride(0)),
                                      ctypes.c_long(conv_off), _p(cu_q), _p(state_slots), _p(out), num_requests, channels,
-                                     taps_w.shape[1], ctypes.c_long(state.shape[0]), _code(x.dtype), _p(err), _stream()),
-           "short_conv_step")
+                                     taps_w.shape[1], ctypes.c_long(state.shape[0]), int(bool(activation)), _code(x.dtype),
+                                     _p(err), _stream()), "short_conv_step")
 
 
 def delta_scan(qkv, ab, b_off: int, a_off: int, A_log, dt_bias, state, cu_q, state_slots, raw, num_requests: int, heads: int,
-               kvh: int, dim: int, vdim: int, err) -> None:
+               kvh: int, dim: int, vdim: int, err, channel_decay: bool = False) -> None:
     """The gated delta rule over every request's tokens of this step, from and to its slot (state [slots, n] float, the
     heads' matrices first, each stored column by column, [heads, vdim, dim]).  qkv float [tokens, 2 kvh dim + heads vdim]; ab: rows whose elements
-    b_off + h and a_off + h are head h's pre-activations of beta and of the decay; raw float [tokens, heads * vdim]."""
+    b_off + h and a_off + h are head h's pre-activations of beta and of the decay; raw float [tokens, heads * vdim].
+    `channel_decay`: the decay has one pre-activation a head and key channel, at a_off + h * dim + d, and dt_bias is
+    [heads * dim]; it multiplies row d of the head's matrix."""
     _cuda(qkv, ab, A_log, dt_bias, state, cu_q, state_slots, raw)
     assert qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[1] == 2 * kvh * dim + heads * vdim
     assert raw.dtype == torch.float32 and raw.is_contiguous() and A_log.dtype == dt_bias.dtype == torch.float32
-    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] >= heads * dim * vdim and ab.stride(1) == 1
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= heads * dim * vdim and ab.stride(1) == 1
+    assert dt_bias.numel() == (heads * dim if channel_decay else heads)
     _check(lib().vob_delta_scan(_p(qkv), _p(ab), ctypes.c_long(ab.stride(0)), b_off, a_off, _p(A_log), _p(dt_bias), _p(state),
                                 ctypes.c_long(state.stride(0)), _p(cu_q), _p(state_slots), _p(raw), num_requests, heads, kvh,
-                                dim, vdim, ctypes.c_long(state.shape[0]), _code(ab.dtype), _p(err), _stream()), "delta_scan")
+                                dim, vdim, ctypes.c_long(state.shape[0]), int(bool(channel_decay)), _code(ab.dtype), _p(err),
+                                _stream()), "delta_scan")
 
 
-def delta_out_norm(raw, gate, weight, out, num_tokens: int, heads: int, vdim: int, eps: float) -> None:
+def delta_out_norm(raw, gate, weight, out, num_tokens: int, heads: int, vdim: int, eps: float, gate_sigmoid: bool = False) -> None:
     """out[t, h] = raw[t, h] / sqrt(mean(raw[t, h]^2) + eps) * weight * SiLU(gate[t, h]) per head over vdim; gate: the
-    first heads * vdim columns of its rows."""
+    first heads * vdim columns of its rows.  `gate_sigmoid`: times sigmoid(gate) instead of SiLU(gate)."""
     _cuda(raw, gate, weight, out)
     assert raw.dtype == torch.float32 and raw.is_contiguous() and out.is_contiguous() and gate.stride(1) == 1
     assert weight.dtype == torch.float32 and gate.dtype == out.dtype
     _check(lib().vob_delta_out_norm(_p(raw), _p(gate), ctypes.c_long(gate.stride(0)), _p(weight), _p(out), num_tokens, heads,
-                                    vdim, ctypes.c_float(eps), _code(out.dtype), _stream()), "delta_out_norm")
+                                    vdim, ctypes.c_float(eps), int(bool(gate_sigmoid)), _code(out.dtype), _stream()), "delta_out_norm")
 
 
 def moe_row_tile() -> int:
@@ -392,17 +476,20 @@ def moe_row_tile() -> int:
 
 
 def moe_route(h, w_router, correction, ids, weights, num_tokens: int, top: int, groups: int, keep: int,
-              sigmoid_scores: bool = False, group_top: int = 1, normalise: bool = False, weight_scale: float = 1.0) -> None:
+              sigmoid_scores: bool = False, group_top: int = 1, normalise: bool = False, weight_scale: float = 1.0,
+              router_bias=None) -> None:
     """ids, weights [tokens, top]: the experts a token uses and their scores (see csrc/kernels/moe.cu): the softmax over
     all experts or (`sigmoid_scores`) a sigmoid each, chosen by score + `correction` (None: by the score) among the `keep`
     groups that count most, a group by its best choice score or (`group_top` 2) by the sum of its two best; the weights
-    are the chosen scores, divided by their sum with `normalise`, times `weight_scale`."""
-    _cuda(h, w_router, correction, ids, weights)
+    are the chosen scores, divided by their sum with `normalise`, times `weight_scale`.  `router_bias` (float [experts]) is
+    added to the logits."""
+    _cuda(h, w_router, correction, ids, weights, router_bias)
+    assert router_bias is None or (router_bias.dtype == torch.float32 and router_bias.is_contiguous())
     E, W = w_router.shape
     assert h.is_contiguous() and h.shape[1] == W and w_router.dtype == torch.float32
     assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous())
     assert w_router.is_contiguous() and ids.dtype == torch.int32 and weights.dtype == torch.float32 and group_top in (1, 2)
-    _check(lib().vob_moe_route(_p(h), _p(w_router), _p(correction), _p(ids), _p(weights), num_tokens, W, E, top, groups, keep,
+    _check(lib().vob_moe_route(_p(h), _p(w_router), _p(router_bias), _p(correction), _p(ids), _p(weights), num_tokens, W, E, top, groups, keep,
                                int(bool(sigmoid_scores)), int(group_top), int(bool(normalise)), ctypes.c_float(weight_scale),
                                _code(h.dtype), _stream()), "moe_route")
 
@@ -426,7 +513,7 @@ def moe_gemm_tc5_supported(a, w) -> bool:
             and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def moe_gemm_tc5(a, w, c, row_token, tile_expert, relu_squared: bool, err, silu_pairs: bool = False) -> None:
+def moe_gemm_tc5(a, w, c, row_token, tile_expert, relu_squared: bool, err, silu_pairs: bool = False, glu_limit: float = 0.0) -> None:
     """c[row] = f(a[row] @ w[expert of the row]^T) on the tcgen05 tensor cores: a [rows, K] bfloat16 already sorted by
     expert in row tiles of moe_tc5_row_tile(), w [experts, N, K]; c bfloat16 with the squared relu, bfloat16 [rows, N / 2]
     with `silu_pairs` (rows of w in (gate, up) pairs: SiLU(gate) * up), or float."""
@@ -436,7 +523,8 @@ def moe_gemm_tc5(a, w, c, row_token, tile_expert, relu_squared: bool, err, silu_
     assert c.dtype == (torch.bfloat16 if relu_squared or silu_pairs else torch.float32) and not (relu_squared and silu_pairs)
     map_w, map_x = tensor_map_2d(w.view(E * N, K), 128), tensor_map_2d(a, 128)
     _check(lib().vob_moe_gemm_tc5(map_w, map_x, _p(c), ctypes.c_long(c.stride(0)), _p(row_token), _p(tile_expert), a.shape[0], N, K,
-                                  2 if silu_pairs else (0 if relu_squared else 1), _p(err), _stream()), "moe_gemm_tc5")
+                                  2 if silu_pairs else (0 if relu_squared else 1), ctypes.c_float(glu_limit), _p(err), _stream()),
+           "moe_gemm_tc5")
 
 
 def moe_gather_rows(x, xs, row_token) -> None:
@@ -447,17 +535,19 @@ def moe_gather_rows(x, xs, row_token) -> None:
                                      _stream()), "moe_gather_rows")
 
 
-def moe_gemm(a, w, c, row_token, tile_expert, relu_squared: bool, gather: bool, silu_pairs: bool = False) -> None:
+def moe_gemm(a, w, c, row_token, tile_expert, relu_squared: bool, gather: bool, silu_pairs: bool = False,
+             glu_limit: float = 0.0) -> None:
     """c[row] = f(a[row or its token] @ w[expert of the row]^T), w [experts, N, K]; float accumulation in one chain.  f: the
     squared relu, or (`silu_pairs`: rows of w in (gate, up) pairs, c [rows, N / 2]) SiLU(gate) * up, both with `gather`
-    into a's type; or the identity into float."""
+    into a's type; or the identity into float.  `glu_limit` > 0 with `silu_pairs`: the clamped form min(gate, limit) *
+    sigmoid(1.702 min(gate, limit)) * (clamp(up, -limit, limit) + 1) (also in moe_gemv and moe_gemm_tc5)."""
     _cuda(a, w, c, row_token, tile_expert)
     assert a.stride(1) == 1 and w.is_contiguous() and c.stride(1) == 1 and a.dtype == w.dtype
     first = relu_squared or silu_pairs
     assert c.dtype == (a.dtype if first else torch.float32) and first == gather and not (relu_squared and silu_pairs)
     _check(lib().vob_moe_gemm(_p(a), ctypes.c_long(a.stride(0)), _p(w), _p(c), ctypes.c_long(c.stride(0)), _p(row_token),
                               _p(tile_expert), row_token.numel(), w.shape[1], w.shape[2], 2 if silu_pairs else int(relu_squared),
-                              int(gather), int(not first),
+                              int(gather), int(not first), ctypes.c_float(glu_limit),
                               _code(a.dtype), _stream()), "moe_gemm")
 
 
@@ -473,7 +563,7 @@ def moe_gemv_supported(a, w, n: int) -> bool:
             and w.is_contiguous() and n <= 65535)
 
 
-def moe_gemv(a, w, c, ids, order, n: int, top: int, relu_squared: bool, silu_pairs: bool = False) -> None:
+def moe_gemv(a, w, c, ids, order, n: int, top: int, relu_squared: bool, silu_pairs: bool = False, glu_limit: float = 0.0) -> None:
     """c[pair] = f(a[pair or its token] @ w[expert of the pair]^T) for the step's pairs, few of them (decoding): bfloat16,
     bound by the experts' rows, which a warp streams with 16-byte loads.  relu_squared: the first product (a by token, c
     bfloat16); else the second (a by pair, c float)."""
@@ -481,8 +571,8 @@ def moe_gemv(a, w, c, ids, order, n: int, top: int, relu_squared: bool, silu_pai
     first = relu_squared or silu_pairs          # silu_pairs: rows of w in (gate, up) pairs, c bfloat16 [pairs, N / 2]
     assert moe_gemv_supported(a, w, n) and c.stride(1) == 1 and c.dtype == (torch.bfloat16 if first else torch.float32)
     _check(lib().vob_moe_gemv(_p(a), ctypes.c_long(a.stride(0)), _p(w), _p(c), ctypes.c_long(c.stride(0)), _p(ids), _p(order), n,
-                              top, w.shape[1], w.shape[2], 2 if silu_pairs else int(relu_squared), int(first), _stream()),
-           "moe_gemv")
+                              top, w.shape[1], w.shape[2], 2 if silu_pairs else int(relu_squared), int(first),
+                              ctypes.c_float(glu_limit), _stream()), "moe_gemv")
 
 
 def moe_combine(y, slot_of, weights, out, num_tokens: int, top: int) -> None:
@@ -582,13 +672,13 @@ def latent_prep(down, wq, wkv, rule, positions, slots, cq, cache, num_tokens: in
     if write_kv:
         assert cache.is_contiguous() and cache.shape[1] == 1 and wkv.dtype == torch.float32 and cache.dtype == down.dtype
         row_width, num_slots = cache.shape[3], cache.shape[0] * cache.shape[2]
-        if rule.rotary_dim > 0 and (rule.frequencies is None or not rule.interleaved):
-            raise KernelError("latent_prep rotates neighbouring pairs by computed angles: the rule needs `frequencies` "
-                              "and `interleaved`")
+        if rule.rotary_dim > 0 and rule.frequencies is None:
+            raise KernelError("latent_prep rotates by computed angles: the rule needs `frequencies`")
     _check(lib().vob_latent_prep(_p(down), ctypes.c_long(down.stride(0)), _p(wq), _p(wkv), _p(rule.frequencies),
                                  ctypes.c_float(rule.amplitude), _p(positions), _p(slots), _p(cq), _p(cache), num_tokens,
                                  q_rank, kv_rank, rot, rule.rotary_dim, row_width, ctypes.c_long(num_slots),
-                                 ctypes.c_float(eps), int(write_kv), _code(down.dtype), _p(err), _stream()), "latent_prep")
+                                 ctypes.c_float(eps), int(write_kv), int(not rule.interleaved), _code(down.dtype), _p(err),
+                                 _stream()), "latent_prep")
 
 
 def latent_query_rotate(q, qa, rule, positions, num_tokens: int, heads: int, dk: int, rot: int, offset: int,
@@ -597,11 +687,11 @@ def latent_query_rotate(q, qa, rule, positions, num_tokens: int, heads: int, dk:
     `rule`; zeros behind, up to row_width."""
     _cuda(q, qa, rule.frequencies, positions)
     assert q.is_contiguous() and qa.is_contiguous() and q.dtype == qa.dtype
-    if rule.rotary_dim > 0 and (rule.frequencies is None or not rule.interleaved):
-        raise KernelError("latent_query_rotate needs a rule with `frequencies` and `interleaved`")
+    if rule.rotary_dim > 0 and rule.frequencies is None:
+        raise KernelError("latent_query_rotate needs a rule with `frequencies`")
     _check(lib().vob_latent_query_rotate(_p(q), _p(qa), _p(rule.frequencies), ctypes.c_float(rule.amplitude), _p(positions),
-                                         num_tokens, heads, dk, rot, rule.rotary_dim, offset, row_width, _code(q.dtype),
-                                         _stream()), "latent_query_rotate")
+                                         num_tokens, heads, dk, rot, rule.rotary_dim, offset, row_width,
+                                         int(not rule.interleaved), _code(q.dtype), _stream()), "latent_query_rotate")
 
 
 def head_linear(x, x_token_stride: int, x_head_stride: int, w, y, y_token_stride: int, y_head_stride: int, num_tokens: int) -> None:

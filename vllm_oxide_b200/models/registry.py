@@ -7,7 +7,8 @@ from __future__ import annotations
 
 from typing import Callable, Dict, Tuple
 
-from ..config.model_config import ConfigError, KesozenConfig, Qwen3Config, RakizenConfig, TofilornConfig
+from ..config.model_config import ConfigError, DepolixConfig, KesozenConfig, Qwen3Config, RakizenConfig, TofilornConfig
+from .depolix import depolix_plan
 from .kesozen import kesozen_plan
 from .plan import ModelPlan
 from .qwen3 import qwen3_plan
@@ -45,3 +46,4 @@ register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict, qwen3_plan)
 register_architecture("Tofilorn", TofilornConfig.from_dict, tofilorn_plan)
 register_architecture("Kesozen", KesozenConfig.from_dict, kesozen_plan)
 register_architecture("Rakizen", RakizenConfig.from_dict, rakizen_plan)
+register_architecture("Depolix", DepolixConfig.from_dict, depolix_plan)

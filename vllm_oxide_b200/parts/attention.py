@@ -205,7 +205,7 @@ class SharedKVAttention(Mixer):
 
 def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: int, kvh: int, hd: int, window: int,
                  scale: float, pairs=None, value_dim=None, sink: bool = False, gate=None, gate_stride: int = 0,
-                 softcap: float = 0.0, chunk: int = 0) -> int:
+                 softcap: float = 0.0, chunk: int = 0, keep_first: int = 0, dist_bias=None) -> int:
     """Attention of every query of the step over the pages of `keys` / `values`; returns the width of a head in `out`.
     bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a portion to the
     tensor-core kernel for portions.  The 32-bit path, and sizes those kernels refuse, go to the plain kernel.
@@ -214,7 +214,9 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
     elements of each head of `out`.  `sink`: the softmax has a silent extra entry of score 0.  `gate`: a view whose element
     [t, h] (rows `gate_stride` apart) is head h's gate of token t; its output is multiplied by the sigmoid of it.
     `softcap` > 0: scores become softcap * tanh(score / softcap); `chunk` > 0: a query sees only keys of its own block of
-    `chunk` positions.  Values of another shape than the keys (their own head size, or fewer heads)
+    `chunk` positions.  `keep_first` > 0: the keys at positions below it are seen by every later query, whatever the window;
+    `dist_bias` (float [rows, heads]): row min(distance, rows - 1) is added to the scaled scores, a learned bias by the distance
+    between query and key.  Values of another shape than the keys (their own head size, or fewer heads)
     go to the plain kernel; values of the keys' head size in a whole fraction of the keys' heads (key
     head k reads value head k / fraction) stay with the tensor-core kernels."""
     tables = ctx.block_tables[group]
@@ -227,10 +229,12 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
     fast = kernels.has_fast_attention(q.dtype, hd, nh // kvh) and scale > 0.0      # the tcgen05 kernel takes maxima before it scales
     fast = fast and not own_values and (FAST_CAP_AND_CHUNK or not (softcap or chunk))
     fast = fast and (out.dtype == q.dtype or (out.dtype == torch.float32 and FAST_CAP_AND_CHUNK))
+    fast = fast and (FAST_KEEP_AND_BIAS or not (keep_first or dist_bias is not None))
     if not fast or ((sink or gate is not None) and not FAST_SINK_AND_GATE):
         kernels.paged_attention_generic(q, q_stride, out, keys, values, tables, ctx.token_req, ctx.positions, T,
                                         nh, kvh, hd, window, scale, ctx.err, value_dim=value_dim, sink=sink, gate=gate,
-                                        gate_stride=gate_stride, softcap=softcap, chunk=chunk)
+                                        gate_stride=gate_stride, softcap=softcap, chunk=chunk, keep_first=keep_first,
+                                        dist_bias=dist_bias)
         return values.shape[3] if own_values else (hd if value_dim is None else value_dim)
     B = ctx.launch_requests
     if ctx.num_decode > 0:
@@ -252,6 +256,8 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
 FAST_SINK_AND_GATE = True
 # Whether they take capped scores, blocks of positions and values with fewer heads than keys (else the plain kernel does).
 FAST_CAP_AND_CHUNK = True
+# Whether they take kept first keys beside a window and a bias by distance (else the plain kernel does).
+FAST_KEEP_AND_BIAS = False
 
 DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)
 

@@ -45,7 +45,8 @@ class CacheSpec:
     its own, [pages, value_heads, block_size, value_dim] (values wider or narrower than keys, or key heads that share a
     value head), and the two tensors are allocated apart.  `chunk` > 0: queries read only keys of their own block of
     `chunk` positions (blocks counted from position 0), so the pages of blocks that lie behind are given back, as those
-    a window has passed.  Planes with equal windows, chunks and page sizes share a group: one page pool and one block
+    a window has passed.  `keep_first` > 0 (with a window or a chunk): the keys at positions below it stay readable for every
+    later query, so their pages are kept.  Planes with equal windows, chunks, kept first positions and page sizes share a group: one page pool and one block
     table per request, whatever their widths, tensors and dtypes."""
     kv_heads: int
     head_dim: int
@@ -56,6 +57,7 @@ class CacheSpec:
     value_heads: Optional[int] = None
     value_dim: Optional[int] = None
     chunk: int = 0
+    keep_first: int = 0
 
     def value_shape(self) -> Tuple[int, int]:
         """(heads, head size) of the second tensor."""

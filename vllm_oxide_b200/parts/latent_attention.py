@@ -21,8 +21,10 @@ A layer with `borrow=True` has no W_dkv and writes nothing: it reads the plane o
 (`ExecStep(..., write_cache=False)`), with its own W_uk, W_uv, queries, window and scale.  The plane's window is the
 largest window of its writer and readers (`cache_window`).
 
-The rotation pairs neighbouring elements and computes its angles from frequencies (a position rule made with
-`table=False`, see parts/rope.py), so there is no largest position.
+The rotation pairs neighbouring elements, or halves (element i with i + rotary_dim / 2) if the position rule says so, and
+computes its angles from frequencies (a position rule made with `table=False`, see parts/rope.py), so there is no largest
+position.  `gate`: the heads side by side are multiplied element by element by sigmoid(W_g h) (<prefix>g, one more block of
+rows in the down product) before the output product.
 """
 from __future__ import annotations
 
@@ -60,7 +62,7 @@ class LatentAttention(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int,
                  scale: float, eps: float, window: Optional[int], position: Optional[str], prefix: str, positions: dict,
-                 dtype, device, borrow: bool = False, cache_window: Optional[int] = None, **_):
+                 dtype, device, borrow: bool = False, cache_window: Optional[int] = None, gate: bool = False, **_):
         self.H, self.nh, self.dk, self.dr, self.dv = int(hidden_size), int(num_heads), int(dim), int(rot_dim), int(vdim)
         self.q_rank, self.kv_rank, self.scale, self.eps = int(q_rank), int(kv_rank), float(scale), float(eps)
         self.window = int(window or 0)
@@ -68,6 +70,7 @@ class LatentAttention(Mixer):
         if self.cache_window and (not self.window or self.window > self.cache_window):
             raise ValueError("a plane must keep at least the keys that its own layer reads")
         self.borrow, self.prefix, self.dtype, self.device = bool(borrow), prefix, dtype, device
+        self.gate, self.gate_off = bool(gate), 0
         if position is not None and position not in positions:
             raise KeyError(f"the plan names position encoding {position!r}, but has only {sorted(positions)}")
         self.rotation = positions[position].rotation_rule() if position is not None else NO_ROTATION
@@ -90,12 +93,20 @@ class LatentAttention(Mixer):
         specs += [TensorSpec(p + "uk", (nh * self.dk, self.kv_rank), "matrix", self.kv_rank),
                   TensorSpec(p + "uv", (nh * self.dv, self.kv_rank), "matrix", self.kv_rank),
                   TensorSpec(p + "o", (H, nh * self.dv), "matrix", nh * self.dv)]
+        if self.gate:
+            specs.append(TensorSpec(p + "g", (nh * self.dv, H), "matrix", H))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         p = self.prefix
         # rows of the query latent, then (a layer with a plane of its own) of the key/value latent and the shared key part
-        self.wdown = (tensors[p + "dq"] if self.borrow else torch.cat([tensors[p + "dq"], tensors[p + "dkv"]], dim=0)).contiguous()
+        rows = [tensors[p + "dq"]] + ([] if self.borrow else [tensors[p + "dkv"]])
+        # the gate's rows follow, from a column that is a multiple of 8 (its reader takes 16-byte pieces where it can)
+        self.gate_off = (sum(r.shape[0] for r in rows) + 7) // 8 * 8
+        if self.gate:
+            pad = self.gate_off - sum(r.shape[0] for r in rows)
+            rows += ([rows[0].new_zeros((pad, self.H))] if pad else []) + [tensors[p + "g"]]
+        self.wdown = torch.cat(rows, dim=0).contiguous()
         self.wq_norm = tensors[p + "dq.norm"].contiguous()
         self.wkv_norm = None if self.borrow else tensors[p + "dkv.norm"].contiguous()
         self.wuq = tensors[p + "uq"].contiguous()
@@ -139,6 +150,8 @@ class LatentAttention(Mixer):
             # the plain kernel packs rows of n * w elements into the buffer, the tensor-core kernels fill its rows
             packed = mixed if w == self.row else mixed.reshape(-1)[:T * n * w].view(T, n * w)
             head_product(packed, w, self.kv_rank, self.wuv[h0:h0 + n], heads[:, h0 * self.dv:(h0 + n) * self.dv], self.dv, T)
+        if self.gate:
+            kernels.sigmoid_gate_mul(heads, down[:, self.gate_off:], nh * self.dv)
         return linear(heads, self.wo, ctx.ws.get("mixer_proj", T, self.H, x.dtype), ctx)
 
 

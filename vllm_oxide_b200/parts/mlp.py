@@ -83,4 +83,49 @@ class SwiGLU(FeedForward):
         return left
 
 
+class ClampedGLU(FeedForward):
+    """down( g * sigmoid(1.702 g) * (u + 1) ) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit); gate and up
+    are one product; `bias`: all three projections have biases (<name>.b), which stay float."""
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, prefix: str, bias: bool = True,
+                 names=("gate", "up", "down"), **_):
+        self.H, self.I, self.limit, self.bias = int(hidden_size), int(intermediate_size), float(limit), bool(bias)
+        if not self.limit > 0.0:
+            raise ValueError(f"the clamp of a gated feed-forward must be positive, not {limit}")
+        self.n_gate, self.n_up, self.n_down = (prefix + n for n in names)
+        self.wgu = self.wdown = self.bgu = self.bdown = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = [TensorSpec(self.n_gate, (self.I, self.H), "matrix", self.H), TensorSpec(self.n_up, (self.I, self.H), "matrix", self.H),
+                 TensorSpec(self.n_down, (self.H, self.I), "matrix", self.I)]
+        if self.bias:
+            specs += [TensorSpec(self.n_gate + ".b", (self.I,), "coefficient", init="small"),
+                      TensorSpec(self.n_up + ".b", (self.I,), "coefficient", init="small"),
+                      TensorSpec(self.n_down + ".b", (self.H,), "coefficient", init="small")]
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.wgu = torch.cat([tensors[self.n_gate], tensors[self.n_up]], dim=0).contiguous()
+        self.wdown = tensors[self.n_down].contiguous()
+        if self.bias:
+            self.bgu = torch.cat([tensors[self.n_gate + ".b"], tensors[self.n_up + ".b"]]).contiguous()
+            self.bdown = tensors[self.n_down + ".b"].contiguous()
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        gu = linear(x, self.wgu, ctx.ws.get("gate_up", T, 2 * self.I, x.dtype), ctx)
+        act = ctx.ws.get("act", T, self.I, x.dtype)
+        kernels.clamped_glu(gu, self.bgu, act, self.limit)
+        out = ctx.ws.get("mlp_out", T, self.H, x.dtype)
+        if x.dtype == torch.float32:
+            kernels.gemm_f32(act, self.wdown, out, bias=self.bdown)
+            return out
+        linear(act, self.wdown, out, ctx)
+        if self.bdown is not None:
+            kernels.add_bias(out, self.bdown)
+        return out
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "glu_clamped", ClampedGLU)

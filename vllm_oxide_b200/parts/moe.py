@@ -15,7 +15,10 @@ Options of `RoutedExperts`, for designs that route otherwise: `activation` "silu
 down(SiLU(gate(x)) * up(x)) (<prefix>e<i>.gate beside up and down; gate and up rows are stored in pairs so that the
 activation is the epilogue of ONE product); `scores` "sigmoid" takes s = sigmoid(z) instead of the softmax; `correction`
 False has no correction tensor (the choice is by s); `group_top` 2 lets a group count by the sum of its two best choice
-scores; `normalise` divides the chosen scores by their sum (+ 1e-20); `weight_scale` multiplies them.
+scores; `normalise` divides the chosen scores by their sum (+ 1e-20); `weight_scale` multiplies them; `router_bias` adds <prefix>router.b to the logits;
+`activation` "glu_clamped" with `limit` makes an expert down(g * sigmoid(1.702 g) * (u + 1)) with g = min(gate(x), limit),
+u = clamp(up(x), -limit, limit).  The softmax over the chosen logits alone is `scores` "softmax" with `normalise` and no
+correction: the chosen shares of the full softmax, divided by their sum.
 """
 from __future__ import annotations
 
@@ -62,18 +65,22 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, expert_size: int, experts: int, top: int, prefix: str, groups: int = 1, keep: int = 1,
                  names=("up", "down", "router", "correction"), activation: str = "relu2", gate_name: str = "gate",
                  scores: str = "softmax", correction: bool = True, group_top: int = 1, normalise: bool = False,
-                 weight_scale: float = 1.0, **_):
+                 weight_scale: float = 1.0, router_bias: bool = False, limit: float = 0.0, **_):
         self.H, self.I, self.E, self.top = int(hidden_size), int(expert_size), int(experts), int(top)
         self.groups, self.keep, self.prefix = int(groups), int(keep), prefix
         if self.E % self.groups or self.keep > self.groups or self.top > (self.E // self.groups) * self.keep:
             raise ValueError(f"{self.E} experts in {self.groups} groups of which {self.keep} are kept cannot give {self.top} choices")
-        if activation not in ("relu2", "silu_gated") or scores not in ("softmax", "sigmoid") or group_top not in (1, 2):
+        if activation not in ("relu2", "silu_gated", "glu_clamped") or scores not in ("softmax", "sigmoid") or group_top not in (1, 2):
             raise ValueError(f"unknown choice among activation {activation!r}, scores {scores!r}, group_top {group_top!r}")
         self.n_up, self.n_down, self.n_router, self.n_correction = names
-        self.n_gate, self.gated = gate_name, activation == "silu_gated"
+        self.n_gate, self.gated = gate_name, activation in ("silu_gated", "glu_clamped")
+        self.limit = float(limit) if activation == "glu_clamped" else 0.0
+        if activation == "glu_clamped" and not self.limit > 0.0:
+            raise ValueError(f"clamped experts need a positive limit, not {limit}")
+        self.has_router_bias = bool(router_bias)
         self.sigmoid_scores, self.has_correction, self.group_top = scores == "sigmoid", bool(correction), int(group_top)
         self.normalise, self.weight_scale = bool(normalise), float(weight_scale)
-        self.wup = self.wdown = self.router = self.correction = None
+        self.wup = self.wdown = self.router = self.correction = self.router_b = None
 
     def _expert(self, e: int, name: str) -> str:
         return f"{self.prefix}e{e}.{name}"
@@ -86,6 +93,8 @@ class RoutedExperts(FeedForward):
             specs += [TensorSpec(self._expert(e, self.n_up), (self.I, self.H), "matrix", self.H),
                       TensorSpec(self._expert(e, self.n_down), (self.H, self.I), "matrix", self.I)]
         specs.append(TensorSpec(self.prefix + self.n_router, (self.E, self.H), "coefficient", self.H, init="normal"))
+        if self.has_router_bias:
+            specs.append(TensorSpec(self.prefix + self.n_router + ".b", (self.E,), "coefficient", init="small"))
         if self.has_correction:
             specs.append(TensorSpec(self.prefix + self.n_correction, (self.E,), "coefficient", init="small"))
         return specs
@@ -100,11 +109,12 @@ class RoutedExperts(FeedForward):
         self.wdown = torch.stack([tensors[self._expert(e, self.n_down)] for e in range(self.E)]).contiguous()
         self.router = tensors[self.prefix + self.n_router].contiguous()
         self.correction = tensors[self.prefix + self.n_correction].contiguous() if self.has_correction else None
+        self.router_b = tensors[self.prefix + self.n_router + ".b"].contiguous() if self.has_router_bias else None
 
     def _route(self, x, ids, weights, T: int) -> None:
         kernels.moe_route(x, self.router, self.correction, ids, weights, T, self.top, self.groups, self.keep,
                           sigmoid_scores=self.sigmoid_scores, group_top=self.group_top, normalise=self.normalise,
-                          weight_scale=self.weight_scale)
+                          weight_scale=self.weight_scale, router_bias=self.router_b)
 
     def forward(self, x, ctx):
         T, top = x.shape[0], self.top
@@ -120,7 +130,7 @@ class RoutedExperts(FeedForward):
             self._route(x, ids, weights, T)
             kernels.moe_order(ids, order, n, self.E)
             act = ctx.ws.get_flat("moe_act", n * self.I, x.dtype).view(n, self.I)
-            kernels.moe_gemv(x, self.wup, act, ids, order, n, top, not self.gated, silu_pairs=self.gated)
+            kernels.moe_gemv(x, self.wup, act, ids, order, n, top, not self.gated, silu_pairs=self.gated, glu_limit=self.limit)
             y = ctx.ws.get_flat("moe_y", n * self.H, torch.float32).view(n, self.H)
             kernels.moe_gemv(act, self.wdown, y, ids, order, n, top, False)
             out = ctx.ws.get("mlp_out", T, self.H, x.dtype)
@@ -139,11 +149,12 @@ class RoutedExperts(FeedForward):
         if fast:
             rows = ctx.ws.get_flat("moe_rows", max_rows * self.H, x.dtype).view(max_rows, self.H)
             kernels.moe_gather_rows(x, rows, row_token)
-            kernels.moe_gemm_tc5(rows, self.wup, act, row_token, tile_expert, not self.gated, ctx.err, silu_pairs=self.gated)
+            kernels.moe_gemm_tc5(rows, self.wup, act, row_token, tile_expert, not self.gated, ctx.err, silu_pairs=self.gated,
+                                 glu_limit=self.limit)
             kernels.moe_gemm_tc5(act, self.wdown, y, row_token, tile_expert, False, ctx.err)
         else:
             kernels.moe_gemm(x, self.wup, act, row_token, tile_expert, relu_squared=not self.gated, gather=True,
-                             silu_pairs=self.gated)
+                             silu_pairs=self.gated, glu_limit=self.limit)
             kernels.moe_gemm(act, self.wdown, y, row_token, tile_expert, relu_squared=False, gather=False)
         out = ctx.ws.get("mlp_out", T, self.H, x.dtype)
         kernels.moe_combine(y, slot_of, weights, out, T, top)

@@ -27,13 +27,15 @@ import torch
 from .base import PositionEncoding, RotationRule, register_part
 
 
-def scaled_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]):
-    """(inv_freq float32 [rotary_dim/2], amplitude) of a rotary encoding, with the stretch of `scaling` if given."""
+def scaled_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict], precise: bool = False):
+    """(inv_freq float32 [rotary_dim/2], amplitude) of a rotary encoding, with the stretch of `scaling` if given.
+    `precise`: the frequencies are computed in float64 and rounded once (else with a float32 power, as the reference's)."""
     half = rotary_dim // 2
-    i = torch.arange(half, dtype=torch.float32)
-    inv_freq = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float32), (2 * i) / rotary_dim)
+    work = torch.float64 if precise else torch.float32
+    i = torch.arange(half, dtype=work)
+    inv_freq = 1.0 / torch.pow(torch.tensor(float(theta), dtype=work), (2 * i) / rotary_dim)
     if not scaling:
-        return inv_freq, 1.0
+        return inv_freq.to(torch.float32), 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
     if factor <= 0 or original <= 0:
         raise ValueError(f"rotary scaling needs a positive factor and original length, got {scaling!r}")
@@ -43,18 +45,19 @@ def scaled_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]):
     lo = max(math.floor(index_of(float(scaling["fast"]))), 0)
     hi = min(math.ceil(index_of(float(scaling["slow"]))), rotary_dim - 1)
     ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
-    return inv_freq / factor * ramp + inv_freq * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+    return (inv_freq / factor * ramp + inv_freq * (1.0 - ramp)).to(torch.float32), 0.1 * math.log(factor) + 1.0
 
 
 class RotaryEmbedding(PositionEncoding):
     def __init__(self, head_dim: int, max_position: int, theta: float, rotary_dim: Optional[int] = None,
-                 interleaved: bool = False, scaling: Optional[dict] = None, table: bool = True, device=None, **_):
+                 interleaved: bool = False, scaling: Optional[dict] = None, table: bool = True, device=None,
+                 precise: bool = False, **_):
         d = head_dim if rotary_dim is None else int(rotary_dim)
         if d % 2 or not 0 < d <= head_dim:
             raise ValueError(f"rotary position encoding needs an even rotary_dim in (0, head_dim {head_dim}], got {d}")
         self.head_dim, self.rotary_dim, self.interleaved = head_dim, d, bool(interleaved)
         self.max_position, self.theta = max_position, float(theta)
-        inv_freq, self.amplitude = scaled_frequencies(d, self.theta, scaling)
+        inv_freq, self.amplitude = scaled_frequencies(d, self.theta, scaling, precise)
         self.cos_sin = self.frequencies = None
         if table:
             t = torch.arange(max_position, dtype=torch.float32)

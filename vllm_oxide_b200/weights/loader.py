@@ -74,8 +74,10 @@ def check_specs(where: str, specs: Iterable[TensorSpec], found: Dict[str, tuple]
     wanted = {s.name: s for s in specs}
     missing = [n for n in wanted if n not in found]
     unexpected = sorted(n for n in found if n not in wanted)
+    # a size of -1 in a spec is read from the checkpoint: any size fits there
+    fits = lambda want, have: len(want) == len(have) and all(w in (-1, h) for w, h in zip(want, have))
     wrong = [(n, tuple(s.shape), tuple(found[n])) for n, s in wanted.items()
-             if n in found and tuple(found[n]) != tuple(s.shape)]
+             if n in found and not fits(tuple(s.shape), tuple(found[n]))]
     if missing or wrong or (strict and unexpected):
         raise WeightsError(where, missing, unexpected, wrong)
     return unexpected

@@ -26,6 +26,9 @@ def _tensor_seed(seed: int, name: str) -> int:
 def random_tensor(spec: TensorSpec, seed: int, scheme: str, device, dtype: torch.dtype) -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, spec.name))
+    if any(n < 0 for n in spec.shape):
+        raise ValueError(f"tensor {spec.name}: a size that is read from a checkpoint cannot be drawn at random; give it in "
+                         f"the configuration")
     if spec.role == "table":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     x = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
