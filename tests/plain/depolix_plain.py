@@ -141,19 +141,18 @@ def window_attention(h, W, p, m, eps, dt):
     k = causal_conv(h @ g("k").T, g("k.conv")).reshape(n, G, dk)
     v = causal_conv(h @ g("v").T, g("v.conv")).reshape(n, G, dv)
     q, k = rms(q, eps), rms(k, eps)
-    rel = g("rel")
-    B, D = rel.shape[0], float(m["bias_max"])
-    size, keep = int(m["mask"]["size"]), int(m["mask"].get("keep_first", 0))
+    rel = g("rel") if p + "rel" in W else None
+    B, D = (rel.shape[0], float(m["bias_max"])) if rel is not None else (0, 0.0)
+    mk = m.get("mask") or {}
+    size, keep = int(mk.get("size") or 0), int(mk.get("keep_first") or 0)
     kh = torch.arange(H) // (H // G)
     s = torch.einsum("ihd,jhd->hij", q, k[:, kh]) * float(m["scale"])
-    bias = torch.zeros((H, n, n), dtype=dt)
-    mask = torch.zeros((n, n), dtype=torch.bool)
-    for i in range(n):
-        for j in range(i + 1):
-            if i - j < size or j < keep:
-                mask[i, j] = True
-                bias[:, i, j] = rel[distance_bucket(i - j, B, D)]
-    s = (s + bias).masked_fill(~mask, float("-inf"))
+    i, j = torch.arange(n)[:, None], torch.arange(n)[None, :]
+    mask = (j <= i) & ((i - j < size) | (j < keep)) if size else (j <= i)
+    if rel is not None:
+        bucket_of = torch.tensor([distance_bucket(d, B, D) for d in range(n)])
+        s = s + rel[bucket_of[(i - j).clamp(min=0)]].permute(2, 0, 1)          # [H, n, n]
+    s = s.masked_fill(~mask, float("-inf"))
     a = torch.softmax(s, dim=-1)
     o = torch.einsum("hij,jhd->ihd", a, v[:, kh])
     o = o * sigmoid(h @ g("g").T)[:, :, None]
@@ -201,10 +200,14 @@ def dense_ff(h, W, p, mlp, dt):
 
 
 def route(h, W, p, top, dt):
-    """(chosen experts [n, top], weights [n, top], logits [n, E])."""
+    """(chosen experts [n, top], weights [n, top], margin [n]: how far the last chosen logit lies above the best one left out)."""
     z = h @ W[p + "router"].to(dt).T + W[p + "router.b"].to(dt)
     vals, idx = torch.topk(z, top, dim=-1)
-    return idx, torch.softmax(vals, dim=-1), z
+    if top < z.shape[-1]:
+        margin = vals[:, -1] - torch.topk(z, top + 1, dim=-1).values[:, -1]
+    else:
+        margin = torch.full((z.shape[0],), float("inf"), dtype=dt)
+    return idx, torch.softmax(vals, dim=-1), margin
 
 
 def expert_ff(h, W, p, limit, dt):
@@ -212,9 +215,11 @@ def expert_ff(h, W, p, limit, dt):
     return clamped_glu(h @ g("gate").T, h @ g("up").T, limit) @ g("down").T
 
 
-def moe_ff(h, W, p, mlp, dt):
+def moe_ff(h, W, p, mlp, dt, margins=None):
     top, limit = int(mlp["router"]["top"]), float(mlp["expert"]["limit"])
-    idx, w, _ = route(h, W, p, top, dt)
+    idx, w, margin = route(h, W, p, top, dt)
+    if margins is not None:
+        margins.append(margin)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(top):
@@ -224,22 +229,26 @@ def moe_ff(h, W, p, mlp, dt):
 
 
 # ---------------------------------------------------------------- the model
-def forward(cfg, W, tokens, dt=torch.float64, layers_out=None):
-    """Logits [n, vocab] of one whole sequence; `layers_out` (a list) receives the stream after every layer."""
+def forward(cfg, W, tokens, dt=torch.float64, layers_out=None, margins=None, noise=None):
+    """Logits [n, vocab] of one whole sequence; `layers_out` (a list) receives the stream after every layer, `margins` (a
+    list) every router's margins [n]; `noise` (a function) is applied to what the sublayers read and return (rounding to 16
+    bits there shows how far a row moves under it)."""
+    noise = noise or (lambda t: t)
     eps, mult = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
     x = W["embed"].to(dt)[torch.as_tensor(tokens, dtype=torch.long)] * float(cfg["embedding"]["scale"])
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
-        h = rms(x, eps) * (1.0 + W[p + "norm1"].to(dt))
+        h = noise(rms(x, eps) * (1.0 + W[p + "norm1"].to(dt)))
         if layer["type"] == "latent_attention":
             y = latent_attention(h, W, p + "mix.", layer["mixer"], eps, dt)
         elif layer["type"] == "parallel":
             y = side_by_side(h, W, p + "mix.", layer["mixer"], eps, dt)
         else:
             raise ValueError(f"unknown layer type {layer['type']!r}")
+        y = noise(y)
         mlp = layer.get("mlp")
         if mlp is not None:
-            y = y + (dense_ff(h, W, p + "mlp.", mlp, dt) if mlp["kind"] == "dense" else moe_ff(h, W, p + "mlp.", mlp, dt))
+            y = y + noise(dense_ff(h, W, p + "mlp.", mlp, dt) if mlp["kind"] == "dense" else moe_ff(h, W, p + "mlp.", mlp, dt, margins))
         x = x + mult * y
         if layers_out is not None:
             layers_out.append(x.clone())

@@ -1,0 +1,569 @@
+"""Depolix through the engine against the plain implementation (tests/plain/depolix_plain.py): every mechanism alone in a
+model of one layer, whole prompts, decoding token by token, portions down to two tokens, unequal requests in one batch
+over pages and state slots that are used again, long decoding across pages and windows, the first tokens, keys far back
+and at the edges of the window and of the kept first tokens, other sizes (also ones that make two sizes equal or 1),
+greedy generation through `LLM`, the replay program and the command line.  The configurations are made here."""
+import json
+import os
+import random
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT
+from plain import depolix_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+def _latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, base=10000.0, dims=None, scaling=None):
+    rot = {"base": base, "dims": rot_dim if dims is None else dims}
+    if scaling:
+        rot["scaling"] = scaling
+    return {"type": "latent_attention", "mixer": dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, q_rank=q_rank,
+                                                      kv_rank=kv_rank, scale=scale, rot=rot)}
+
+
+def _sides(left, right):
+    return {"type": "parallel", "mixer": {"left": left, "right": right}}
+
+
+def _left(heads, kv_heads, dim, vdim, conv, scale, size, keep, rows, bias_max):
+    return dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv, scale=scale, bias_rows=rows, bias_max=bias_max,
+                mask=dict(size=size, keep_first=keep))
+
+
+def _right(heads, kv_heads, dim, vdim, conv, decay_rank, gate_rank):
+    return dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv, decay_rank=decay_rank, gate_rank=gate_rank)
+
+
+def _dense(layer, ff, limit):
+    return dict(layer, mlp={"kind": "dense", "ff": ff, "limit": limit})
+
+
+def _moe(layer, ff, limit, experts, top):
+    return dict(layer, mlp={"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}})
+
+
+def _none(layer):
+    return dict(layer, mlp=None)
+
+
+def _model(vocab, width, eps, layers, scale=1.0, mult=1.0, logit_scale=1.0):
+    return {"architecture": "Depolix", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": scale},
+            "residual_mult": mult, "logit_scale": logit_scale, "layers": layers}
+
+
+YARN = {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}
+
+CONFIGS = {
+    # both kinds of layer and of feed-forward; a window shorter than two pages that keeps a few first tokens; three query heads
+    # on one key head; the delta rule's heads share keys in pairs; stretched frequencies; pages of 16
+    "A": dict(block_size=16, config=_model(173, 80, 1e-5, [
+        _dense(_latent(3, 24, 8, 20, 28, 40, 0.2, 5000.0, scaling=YARN), 120, 1.5),
+        _moe(_sides(_left(3, 1, 24, 40, 3, 0.25, 21, 5, 12, 90.0), _right(4, 2, 16, 24, 4, 12, 8)), 40, 2.0, 6, 2),
+        _none(_latent(2, 16, 16, 16, 20, 32, 0.3, 100.0, dims=8)),
+        _dense(_sides(_left(2, 2, 16, 16, 2, 0.3, 40, 0, 8, 30.0), _right(2, 2, 24, 8, 2, 4, 4)), 64, 3.0)], 3.5, 0.5, 0.7)),
+    # head sizes the tensor-core kernels take; as many key heads as heads; one expert chosen; a window of one page that keeps a
+    # whole page and three tokens; nothing of the shared part left unrotated; pages of 64
+    "B": dict(block_size=64, config=_model(384, 128, 1e-6, [
+        _moe(_sides(_left(4, 4, 64, 64, 4, 0.125, 64, 67, 32, 240.0), _right(2, 1, 64, 64, 3, 16, 16)), 64, 1.0, 5, 1),
+        _dense(_latent(4, 64, 32, 64, 48, 96, 0.11, 500000.0, scaling={"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0}), 192, 1.5),
+        _moe(_latent(2, 32, 64, 48, 64, 64, 0.09, 10000.0), 48, 2.5, 4, 4)], 11.3, 1.0, 0.5)),
+    # one head everywhere; a window of one position (a token sees itself and the kept first); filters of one tap (no state) and
+    # of six; every expert chosen; kept first tokens beyond the window's reach from the start; sizes that are no multiples of 8
+    "C": dict(block_size=32, config=_model(97, 100, 1e-5, [
+        _moe(_sides(_left(1, 1, 20, 12, 1, 0.4, 1, 3, 6, 17.0), _right(1, 1, 12, 20, 6, 3, 5)), 30, 2.0, 3, 3),
+        _dense(_latent(1, 12, 6, 28, 10, 18, 0.35, 777.0, dims=4), 150, 0.75),
+        _none(_sides(_left(5, 5, 12, 28, 5, 0.2, 90, 33, 16, 64.0), _right(6, 3, 20, 12, 4, 7, 9)))], 1.0, 0.25, 2.0)),
+}
+NAMES = sorted(CONFIGS)
+DTYPES = ["float32", "bfloat16"]
+def kept_float(name):
+    """Tensors that the engine keeps in float on both paths: norm gains, filters, rates, the distance table, routers, and the
+    feed-forwards' biases (the delta rule's `.b` is a matrix, the projection of beta)."""
+    if name.endswith((".conv", "A_log", "dt_bias", ".rel", ".out", "router", "router.b", "norm", "norm1")):
+        return True
+    return name.endswith(".b") and ".mlp." in name
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {name: random_folders(tmp_path_factory.mktemp(f"depolix_{name}"), spec["config"], 71 + k)
+            for k, (name, spec) in enumerate(sorted(CONFIGS.items()))}
+
+
+_models, _truth = {}, {}
+
+
+def tokens_for(name, n, salt=0):
+    g = torch.Generator().manual_seed(9001 * (NAMES.index(name) + 1) + salt)
+    return torch.randint(0, CONFIGS[name]["config"]["vocab"], (n,), generator=g).tolist()
+
+
+def as_held(w, dtype):
+    """The weights as the engine holds them: matrices rounded to bfloat16 on that path, the rest float."""
+    if dtype == "float32":
+        return w
+    return {k: (v if kept_float(k) or not v.dtype.is_floating_point else v.to(torch.bfloat16).to(v.dtype)) for k, v in w.items()}
+
+
+CLOSE_CALL = 0.05     # a router's choice that logits moved by this much would turn over is not held against bfloat16
+TIE = 1e-5            # ... and one that this much would turn over not against 32 bits either
+
+
+class Rows(np.ndarray):
+    """Logits with, per row, whether a router's choice at or before it was a close call (`unsure`) and how far rounding what
+    the sublayers read and return to 16 bits moves the row, as a share of its spread (`moved`)."""
+
+
+def to_16_bits(t):
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+def plain_logits(cfg, w, tokens):
+    margins = []
+    exact = P.forward(cfg, w, tokens, torch.float64, margins=margins).numpy()
+    out = exact.view(Rows)
+    least = torch.stack(margins).min(0).values.numpy() if margins else np.full(len(tokens), np.inf)
+    # a close call turns an expert over, and every later row may read what that row left in keys or in a state
+    out.unsure = np.minimum.accumulate(least) < CLOSE_CALL
+    ties = np.nonzero(least < TIE)[0]
+    out.sure_rows = int(ties[0]) if len(ties) else len(tokens)
+    rounded = P.forward(cfg, w, tokens, torch.float64, noise=to_16_bits).numpy()
+    out.moved = np.sqrt(((rounded - exact) ** 2).mean(-1)) / exact.std(-1)
+    return out
+
+
+# A random router's logits lie close together, and rounding to bfloat16 turns a choice over every few dozen tokens.  So the
+# two precisions get folders of their own, equal but for the routers: times five for the 32-bit runs (choices that differ
+# from token to token, held exactly); for bfloat16 a small matrix under biases that lie four apart, so that the biases choose
+# (the same experts for every token, with weights that still differ) and no choice is close.
+def random_folders(folder, config, seed):
+    """{dtype: folder} of one random model."""
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    from vllm_oxide_b200.weights.safetensors_io import write_safetensors
+    out = {}
+    for dtype in DTYPES:
+        out[dtype] = os.path.join(str(folder), dtype)
+        write_random_model_folder(out[dtype], config, seed, "fan_in", torch.float32)
+        _, w = P.read_folder(out[dtype])
+        for k in list(w):
+            if k.endswith("router"):
+                w[k] = w[k] * (5.0 if dtype == "float32" else 0.3)
+            elif k.endswith("router.b") and dtype == "bfloat16":
+                g = torch.Generator().manual_seed(seed + len(k))
+                w[k] = 4.0 * torch.randperm(w[k].numel(), generator=g).to(w[k].dtype)
+            elif k.endswith("A_log"):
+                w[k] = w[k] - 2.0            # heads that forget slowly, so that a lost state shows
+        write_safetensors(os.path.join(out[dtype], "model.safetensors"), w)
+    return out
+
+
+def truth(folders, name, tokens, dtype):
+    key = (name, tuple(tokens), dtype)
+    if key not in _truth:
+        if (name, dtype) not in _models:
+            cfg, w = P.read_folder(folders[name][dtype])
+            _models[(name, dtype)] = (cfg, as_held(w, dtype))
+        _truth[key] = plain_logits(*_models[(name, dtype)], tokens)
+    return _truth[key]
+
+
+def close(got, want, dtype, what):
+    """float32: within 1e-4 of the logits' spread, row by row (rounding alone stays near 1e-6; a wrong key, gate, expert,
+    state or mask moves a row by percents).  bfloat16: within 0.1 of it, wider where the plain run itself moves when its
+    sublayers round to 16 bits, and except for rows from a router's close call on."""
+    unsure, moved, sure_rows = getattr(want, "unsure", None), getattr(want, "moved", None), getattr(want, "sure_rows", None)
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert got.shape == want.shape, what
+    err = np.sqrt(((got - want) ** 2).mean(-1)) / want.std(-1)
+    if dtype == "float32":
+        if sure_rows is not None and len(unsure) == len(err):
+            err = err[:sure_rows]
+        if len(err) == 0:
+            return
+        assert err.max() < 1e-4, f"{what}: row {int(err.argmax())} is {err.max():.3e} of the spread off"
+        return
+    sure = np.ones(len(err), bool) if unsure is None or len(unsure) != len(err) else ~unsure
+    bound = 0.1 + 5.0 * moved if moved is not None and len(moved) == len(err) else np.full(len(err), 0.1)
+    worst = np.where(sure, err / bound, 0.0)
+    assert worst.max() < 1.0, f"{what}: row {int(worst.argmax())} is {err[worst.argmax()]:.3e} of the spread off"
+    if sure.sum() >= 8:
+        assert np.median(err[sure]) < 0.05, f"{what}: half of the rows are more than {np.median(err[sure]):.3e} of the spread off"
+
+
+def pick(rows, which):
+    out = np.asarray(rows)[which].view(Rows)
+    out.unsure, out.moved, out.sure_rows = rows.unsure[which], rows.moved[which], None
+    return out
+
+
+def runner(folders, name, dtype, max_tokens, max_live=4):
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    return TraceRunner(folders[name][dtype], dtype, max_tokens, CONFIGS[name]["block_size"], max_live=max_live)
+
+
+def feed(r, rid, tokens, cuts):
+    """Feeds `tokens` in portions of the sizes `cuts` (cycled); logits at every position."""
+    rows, at, k = [], 0, 0
+    while at < len(tokens):
+        n = min(cuts[k % len(cuts)], len(tokens) - at)
+        k += 1
+        end = [rid] if at + n == len(tokens) else []
+        rows.append(r.step([{"id": rid, "tokens": tokens[at:at + n], "want": list(range(n))}], end))
+        at += n
+    return np.concatenate(rows, 0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_then_decoded_then_in_portions(folders, name, dtype):
+    toks = tokens_for(name, 150)
+    want = truth(folders, name, toks, dtype)
+    r = runner(folders, name, dtype, 256)
+    whole = feed(r, "w", toks, [len(toks)])
+    close(whole, want, dtype, f"{name} {dtype} whole")
+    decoded = feed(r, "d", toks, [len(toks) - 60] + [1] * 60)
+    close(decoded, want, dtype, f"{name} {dtype} last 60 tokens one by one")
+    for cuts in ([2], [3, 1, 17, 2, 64, 5], [CONFIGS[name]["block_size"]], [1, 2], [9]):
+        got = feed(r, "p", toks, cuts)
+        close(got, want, dtype, f"{name} {dtype} portions {cuts}")
+        if dtype == "float32":
+            assert np.abs(got - whole).max() <= 2e-5 * np.abs(whole).max(), f"{name} portions {cuts} against whole"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_token_by_token_from_the_first(folders, name, dtype):
+    toks = tokens_for(name, 120, salt=5)
+    r = runner(folders, name, dtype, 128)
+    close(feed(r, "t", toks, [1]), truth(folders, name, toks, dtype), dtype, f"{name} {dtype} every token alone")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens_of_a_sequence(folders, name, dtype):
+    r = runner(folders, name, dtype, 64)
+    for n in (1, 2, 3, 4, 6):
+        toks = tokens_for(name, n, salt=40 + n)
+        close(feed(r, f"f{n}", toks, [n]), truth(folders, name, toks, dtype), dtype, f"{name} {dtype} a prompt of {n}")
+        close(feed(r, f"g{n}", toks, [1]), truth(folders, name, toks, dtype), dtype, f"{name} {dtype} {n} single tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_requests_in_one_batch_over_pages_and_slots_used_again(folders, name, dtype):
+    """Nine requests, at most three live over three state slots, over a pool that holds far less than all of them: portions
+    of some beside single tokens of others; a finished request's pages and slot go to the next one."""
+    rng = random.Random(NAMES.index(name))
+    bs = CONFIGS[name]["block_size"]
+    lengths = [70, 1, 33, 130, 2, 64, 97, 18, 150]
+    reqs = {f"q{i}": tokens_for(name, n, salt=100 + i) for i, n in enumerate(lengths)}
+    live_cap = 3
+    pool = sum(sorted(((n + bs - 1) // bs * bs for n in lengths), reverse=True)[:live_cap])
+    r = runner(folders, name, dtype, pool, max_live=live_cap)
+    free_pages = lambda: [r.manager.num_free_blocks(g) for g in range(r.manager.num_groups)]
+    free_at_start = free_pages()
+    waiting, live, at, got = list(reqs), [], {}, {k: [] for k in reqs}
+    while waiting or live:
+        while waiting and len(live) < live_cap:
+            live.append(waiting.pop(0))
+            at[live[-1]] = 0
+        entries, end = [], []
+        for rid in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                              # left out of this step, goes on later
+            left = len(reqs[rid]) - at[rid]
+            n = min(left, rng.choice([1, 1, 2, 3, 7, bs, bs + 5, 40]))
+            entries.append({"id": rid, "tokens": reqs[rid][at[rid]:at[rid] + n], "want": list(range(n))})
+            at[rid] += n
+            if at[rid] == len(reqs[rid]):
+                end.append(rid)
+                live.remove(rid)
+        if not entries:
+            continue
+        out = r.step(entries, end)
+        k = 0
+        for e in entries:
+            got[e["id"]].append(out[k:k + len(e["tokens"])])
+            k += len(e["tokens"])
+    assert free_pages() == free_at_start, "every page came back"
+    assert r.manager.num_free_state_slots == live_cap, "every slot came back"
+    for rid, toks in reqs.items():
+        close(np.concatenate(got[rid], 0), truth(folders, name, toks, dtype), dtype, f"{name} {dtype} request {rid} in mixed batches")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_across_pages_and_windows(folders, dtype):
+    for name in ("A", "C"):
+        toks = tokens_for(name, 330, salt=9)
+        r = runner(folders, name, dtype, 384)
+        close(feed(r, "l", toks, [6] + [1] * 324), truth(folders, name, toks, dtype), dtype, f"{name} {dtype} 324 decoded tokens")
+
+
+# ---------------------------------------------------------------- every mechanism alone, in a model of one layer
+ALONE = {
+    "latent attention": _none(_latent(3, 16, 8, 24, 12, 20, 0.3, 1000.0, scaling=YARN)),
+    "latent attention, part of the shared key unrotated": _none(_latent(2, 8, 12, 8, 16, 24, 0.4, 50.0, dims=6)),
+    "window attention beside a silent delta rule": _none(_sides(_left(4, 2, 16, 24, 3, 0.3, 19, 4, 10, 50.0), _right(1, 1, 8, 8, 2, 2, 2))),
+    "delta rule beside a silent window attention": _none(_sides(_left(1, 1, 8, 8, 2, 0.3, 5, 0, 4, 9.0), _right(4, 2, 24, 16, 4, 6, 5))),
+    "dense feed-forward": _dense(_latent(1, 8, 4, 8, 8, 8, 0.3), 56, 0.8),
+    "experts": _moe(_latent(1, 8, 4, 8, 8, 8, 0.3), 24, 1.2, 7, 3),
+}
+
+
+@pytest.mark.parametrize("what", sorted(ALONE))
+def test_every_mechanism_alone(what, tmp_path):
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    from vllm_oxide_b200.weights.safetensors_io import write_safetensors
+    cfg = _model(90, 48, 1e-5, [ALONE[what]], 2.0, 0.5, 1.5)
+    dirs = random_folders(tmp_path, cfg, 300 + sorted(ALONE).index(what))
+    toks = torch.randint(0, 90, (100,), generator=torch.Generator().manual_seed(5)).tolist()
+    for dtype in DTYPES:
+        c, w = P.read_folder(dirs[dtype])
+        if "silent delta" in what:
+            w["l0.mix.right.out"].zero_()
+        if "silent window" in what:
+            w["l0.mix.left.out"].zero_()
+        if what == "dense feed-forward" or what == "experts":
+            w["l0.mix.o"].mul_(0.05)               # the feed-forward carries the row
+            for k in w:
+                if k.endswith(".b") and "router" not in k:
+                    w[k] = 3.0 * w[k]              # biases large enough to show, and values beyond the clamp on both sides
+        write_safetensors(os.path.join(dirs[dtype], "model.safetensors"), w)
+        want = plain_logits(c, as_held(w, dtype), toks)
+        r = TraceRunner(dirs[dtype], dtype, 128, 16, max_live=2)
+        for cuts in ([len(toks)], [len(toks) - 30] + [1] * 30, [3, 1, 17, 2, 40], [2]):
+            close(feed(r, "x", toks, cuts), want, dtype, f"{what}, {dtype}, cuts {cuts[:5]}")
+
+
+# ---------------------------------------------------------------- loud keys: what a query sees
+def _loud_window_model(tmp_path, left, seed):
+    """A model of one side-by-side layer whose delta rule is silent and whose filters pass the current token alone, in which
+    token 45's key and token 46's query point the same way and tower over the rest: the row behind a query token hangs on
+    whether a key token is visible to it."""
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    from vllm_oxide_b200.weights.safetensors_io import write_safetensors
+    cfg = _model(50, 64, 1e-6, [_none(_sides(left, _right(1, 1, 8, 8, 2, 2, 2)))])
+    write_random_model_folder(str(tmp_path), cfg, seed, "fan_in", torch.float32)
+    cfg, w = P.read_folder(str(tmp_path))
+    g = torch.Generator().manual_seed(seed + 5)
+    d_key, d_query = torch.nn.functional.normalize(torch.randn(2, 64, generator=g), dim=-1)
+    w["embed"][45], w["embed"][46] = 8.0 * d_key, 8.0 * d_query
+    w["l0.norm1"].zero_()
+    w["l0.mix.right.out"].zero_()
+    for n in ("q", "k", "v"):
+        c = w[f"l0.mix.left.{n}.conv"]
+        c.zero_()
+        c[:, -1] = 1.0
+    # every row of the first key head and of its query heads reads the loud direction: after the unit norm the two heads
+    # point the same way, and their score is the head size times the scale
+    dim = left["dim"]
+    w["l0.mix.left.k"][:dim] = d_key[None, :] + 0.05 * w["l0.mix.left.k"][:dim]
+    w["l0.mix.left.q"][:dim] = d_query[None, :] + 0.05 * w["l0.mix.left.q"][:dim]
+    w["l0.mix.left.rel"].mul_(0.2)
+    write_safetensors(str(tmp_path / "model.safetensors"), w)
+    return cfg, w
+
+
+def _edge_case(cfg, w, dtype, toks, query_at, key_at, seen, what):
+    """The plain model's row at `query_at` moves when the token at `key_at` is another one if and only if `seen`."""
+    want = P.forward(cfg, as_held(w, dtype), toks, torch.float64).numpy()
+    other = list(toks)
+    other[key_at] = 44
+    gap = np.abs(P.forward(cfg, as_held(w, dtype), other, torch.float64).numpy()[query_at] - want[query_at]).max()
+    if seen:
+        assert gap > 0.2 * want[query_at].std(), f"{what}: the plain row hangs on the key"
+    else:
+        assert gap == 0.0, f"{what}: the plain row does not see the key"
+    return want
+
+
+def test_keys_at_the_edges_of_the_window_and_of_the_kept_first_tokens(tmp_path):
+    """The loud key sits just inside and just outside the window of the loud query, far back inside it, at a page border,
+    and among the kept first tokens, on the last of them and on the first that is not kept; the query comes in a prompt's
+    portion or decoded alone.  The engine follows the plain model in every cut."""
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    size, keep, page, n = 300, 70, 64, 700
+    cfg, w = _loud_window_model(tmp_path, _left(2, 1, 64, 48, 3, 1.0, size, keep, 32, 400.0), 3)
+    query_at = n - 1
+    first = query_at - size + 1
+    cases = [(first, True, "the first key that is seen"), (first - 1, False, "the key before it"),
+             (first + 37, True, "far back, seen"), (first - 1 - page, False, "a page further out"),
+             (query_at - 1, True, "the key next to the query"), (first // page * page + page, True, "the first key of a page inside"),
+             (keep - 1, True, "the last kept first token"), (keep, False, "the first token that is not kept"),
+             (0, True, "the first token of all"), (63, True, "the last token of the first page"), (64, True, "a kept token on the second page")]
+    for dtype in DTYPES:
+        r = TraceRunner(str(tmp_path), dtype, 1024, page, max_live=2)
+        for key_at, seen, what in cases:
+            toks = [1 + (i % 40) for i in range(n)]
+            toks[key_at], toks[query_at] = 45, 46
+            want = _edge_case(cfg, w, dtype, toks, query_at, key_at, seen, what)
+            for cuts in ([n], [query_at, 1], [100, 2, 64], [key_at + 1, query_at - key_at - 1, 1], [query_at - 1, 2]):
+                cuts = [c for c in cuts if c > 0]
+                close(feed(r, "x", toks, cuts), want, dtype, f"{what}, {dtype}, cuts {cuts}")
+        # every page behind the window went back while the request ran, except the kept ones: at the end all are free
+        assert r.manager.num_free_blocks(0) == 1024 // page
+
+
+def test_a_far_key_among_hundreds_in_latent_attention(tmp_path):
+    """A factor on the scores that makes every softmax all but one-hot: each row hangs on one key somewhere among the
+    hundreds before it, and on the right rotation of that key's shared part."""
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    cfg = _model(120, 64, 1e-5, [_none(_latent(4, 16, 16, 16, 24, 32, 6.0, 10000.0, scaling=YARN))])
+    dirs = random_folders(tmp_path, cfg, 17)
+    toks = torch.randint(0, 120, (600,), generator=torch.Generator().manual_seed(3)).tolist()
+    c, w = P.read_folder(dirs["float32"])
+    want = plain_logits(c, w, toks)
+    flat = dict(c, layers=[dict(c["layers"][0], mixer=dict(c["layers"][0]["mixer"], scale=0.01))])
+    assert np.abs(P.forward(flat, w, toks, torch.float64).numpy() - want).max() > 0.5 * want.std()
+    r = TraceRunner(dirs["float32"], "float32", 640, 64, max_live=2)
+    for cuts in ([600], [560] + [1] * 40, [100, 2, 64, 3]):
+        close(feed(r, "x", toks, cuts), want, "float32", f"far keys, cuts {cuts[:4]}")
+
+
+def test_the_delta_rule_keeps_its_state_over_hundreds_of_tokens(tmp_path):
+    """Heads that all but never forget: the last rows hang on what the first tokens wrote into the state."""
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    from vllm_oxide_b200.weights.safetensors_io import write_safetensors
+    cfg = _model(80, 48, 1e-5, [_none(_sides(_left(1, 1, 8, 8, 2, 0.3, 4, 0, 4, 9.0), _right(3, 3, 16, 12, 4, 5, 6)))])
+    dirs = random_folders(tmp_path, cfg, 23)
+    toks = torch.randint(0, 80, (400,), generator=torch.Generator().manual_seed(8)).tolist()
+    for dtype in DTYPES:
+        c, w = P.read_folder(dirs[dtype])
+        w["l0.mix.right.A_log"].fill_(-6.0)
+        w["l0.mix.left.out"].zero_()
+        write_safetensors(os.path.join(dirs[dtype], "model.safetensors"), w)
+        held = as_held(w, dtype)
+        want = plain_logits(c, held, toks)
+        other = [(t + 1) % 80 for t in toks[:5]] + toks[5:]
+        assert np.abs(P.forward(c, held, other, torch.float64).numpy()[-1] - want[-1]).max() > 0.05 * want[-1].std()
+        r = TraceRunner(dirs[dtype], dtype, 448, 32, max_live=2)
+        for cuts in ([400], [370] + [1] * 30, [50, 2, 31]):
+            close(feed(r, "x", toks, cuts), want, dtype, f"long memory, {dtype}, cuts {cuts[:3]}")
+
+
+# ---------------------------------------------------------------- other sizes
+def random_configuration(seed):
+    """A configuration drawn from a seeded generator: two to four layers of either kind in any order, head counts, sizes that
+    are equal, unequal, 1, multiples of 16 or not, windows shorter and longer than a page with and without kept first tokens,
+    every kind of feed-forward."""
+    rng = random.Random(seed)
+    layers = []
+    for _ in range(rng.randint(2, 4)):
+        if rng.random() < 0.5:
+            rot_dim = rng.choice([2, 4, 8, 16])
+            layer = _latent(rng.choice([1, 2, 3, 5]), rng.choice([4, 8, 16, 24]), rot_dim, rng.choice([4, 8, 20, 32]),
+                            rng.choice([4, 9, 16]), rng.choice([8, 12, 32, 48]), rng.choice([0.05, 0.15, 0.3]),
+                            rng.choice([100.0, 1e4, 5e5]), dims=rng.choice([rot_dim, rot_dim, max(2, rot_dim // 2)]),
+                            scaling=rng.choice([None, YARN, {"factor": 8.0, "original": 100, "fast": 4.0, "slow": 1.0}]))
+        else:
+            kv = rng.choice([1, 2, 3])
+            rows = rng.choice([2, 6, 8, 16, 32])
+            left = _left(kv * rng.choice([1, 2, 4]), kv, rng.choice([8, 16, 24, 64]), rng.choice([8, 16, 40, 64]), rng.choice([1, 2, 3, 4]),
+                         rng.choice([0.05, 0.2, 0.4]), rng.choice([1, 5, 16, 23, 64, 100]), rng.choice([0, 0, 1, 4, 16, 70]), rows,
+                         float(rows // 2 + rng.choice([1, 7, 50, 300])))
+            kv = rng.choice([1, 2])
+            right = _right(kv * rng.choice([1, 2, 3]), kv, rng.choice([8, 16, 40, 64]), rng.choice([4, 8, 16, 36]), rng.choice([1, 2, 4, 5]),
+                           rng.choice([1, 4, 16]), rng.choice([1, 3, 8]))
+            layer = _sides(left, right)
+        kind = rng.choice(["none", "dense", "moe", "moe"])
+        if kind == "none":
+            layer = _none(layer)
+        elif kind == "dense":
+            layer = _dense(layer, rng.choice([24, 64, 100]), rng.choice([0.5, 1.5, 7.0]))
+        else:
+            experts = rng.choice([2, 3, 5, 8])
+            layer = _moe(layer, rng.choice([8, 24, 40]), rng.choice([0.5, 2.0]), experts, rng.randint(1, min(3, experts)))
+        layers.append(layer)
+    cfg = _model(rng.choice([61, 128, 300]), rng.choice([32, 48, 72, 128]), rng.choice([1e-5, 1e-6]), layers,
+                 rng.choice([1.0, 5.7]), rng.choice([1.0, 0.5, 0.3]), rng.choice([1.0, 0.5, 1.3]))
+    return cfg, rng.choice([16, 32, 64])
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_configurations(seed, tmp_path):
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    cfg, page = random_configuration(2000 + seed)
+    dirs = random_folders(tmp_path, cfg, seed)
+    g = torch.Generator().manual_seed(seed)
+    toks = torch.randint(0, cfg["vocab"], (140,), generator=g).tolist()
+    for dtype in DTYPES:
+        c, w = P.read_folder(dirs[dtype])
+        want = plain_logits(c, as_held(w, dtype), toks)
+        r = TraceRunner(dirs[dtype], dtype, 192, page, max_live=2)
+        for cuts in ([len(toks)], [len(toks) - 30] + [1] * 30, [3, 1, 17, 2, 40]):
+            close(feed(r, "x", toks, cuts), want, dtype, f"random configuration {seed}, {dtype}, cuts {cuts[:5]}")
+
+
+# ---------------------------------------------------------------- generation, the replay program, the command line
+def plain_greedy(folders, name, prompt, new):
+    toks = list(prompt)
+    for _ in range(new):
+        toks.append(int(truth(folders, name, toks, "float32")[-1].argmax()))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation_through_the_engine(folders, name):
+    """`LLM.generate`: the scheduler cuts prompts to its token budget, batches them with decoding requests and preempts
+    when the pool runs dry; the tokens are the plain implementation's."""
+    from vllm_oxide_b200 import LLM, EngineOptions, SamplingParams
+    bs = CONFIGS[name]["block_size"]
+    llm = LLM(folders[name]["float32"], EngineOptions(dtype="float32", block_size=bs, num_kv_blocks=max(6, 320 // bs), max_num_seqs=3,
+                                                      max_num_batched_tokens=48, max_model_len=256))
+    prompts = [tokens_for(name, n, salt=300 + n) for n in (5, 61, 1, 100, 17)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain_greedy(folders, name, p, 10), f"{name}: a prompt of {len(p)}"
+
+
+def test_bfloat16_generation_runs_from_graphs_and_agrees_where_the_plain_run_is_sure(folders):
+    from vllm_oxide_b200 import LLM, EngineOptions, SamplingParams
+    name = "B"
+    llm = LLM(folders[name]["bfloat16"], EngineOptions(dtype="bfloat16", block_size=64, num_kv_blocks=16, max_num_seqs=4, max_model_len=512))
+    prompts = [tokens_for(name, n, salt=500 + n) for n in (9, 70, 130)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+    assert llm.core.graph_replays > 0
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        for t in o.token_ids:
+            row = truth(folders, name, toks, "bfloat16")[-1]
+            top = np.sort(row)[-2:]
+            if top[1] - top[0] < 0.1 * row.std():
+                break                                  # too close to call in bfloat16: the runs may part here
+            assert t == int(row.argmax())
+            toks.append(t)
+
+
+def test_the_replay_program(folders, tmp_path):
+    name = "A"
+    toks = tokens_for(name, 50, salt=77)
+    other = tokens_for(name, 21, salt=78)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[30:32], "want": []}, {"id": "b", "tokens": other, "want": [20]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": toks[32:], "want": [17]}], "end": ["a"]}]
+    for dtype in DTYPES:
+        out = tmp_path / dtype
+        p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folders[name][dtype], "--dtype", dtype, "--out", str(out),
+                            "--max-tokens", "128", "--block-size", "16"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                           capture_output=True, text=True, timeout=1200)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+        want = truth(folders, name, toks, dtype)
+        close(np.fromfile(out / "0.f32", "<f4").reshape(2, -1), pick(want, [0, 29]), dtype, "step 0")
+        close(np.fromfile(out / "1.f32", "<f4").reshape(1, -1), pick(truth(folders, name, other, dtype), [20]), dtype, "step 1")
+        close(np.fromfile(out / "2.f32", "<f4").reshape(1, -1), pick(want, [49]), dtype, "step 2")
+
+
+def test_the_command_line(folders):
+    name = "C"
+    prompt = tokens_for(name, 9, salt=900)
+    p = subprocess.run([os.path.join(ROOT, "bin", "vllm-oxide"), "-m", folders[name]["float32"], "--token-ids", " ".join(map(str, prompt)),
+                        "--max-tokens", "6", "--dtype", "float32", "--ignore-eos", "--max-model-len", "128", "--block-size", "32",
+                        "--num-kv-blocks", "16"], capture_output=True, text=True, timeout=1200)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(t) for t in p.stdout.split()] == plain_greedy(folders, name, prompt, 6)
