@@ -124,7 +124,8 @@ class ConvBiasAttention(Mixer):
         proj = linear(x, self.w_in, ctx.ws.get("conv_attn_in", T, self.width, x.dtype), ctx)
         qkv = ctx.ws.get("conv_attn_qkv", T, self.channels, torch.float32)
         if state is None:
-            state = ctx.ws.get_flat("conv_attn_no_state", 1, torch.float32, zero=True).view(1, 1)     # one tap: nothing is kept
+            # one tap: nothing is kept, and no slot is read; every slot number finds the same empty row
+            state = ctx.ws.get_flat("conv_attn_no_state", 1, torch.float32, zero=True).view(1, 1).expand(1 << 30, 1)
         if ctx.max_q <= SHORT_PORTIONS:
             kernels.short_conv_step(proj, self.channels, self.conv_w, state, 0, ctx.cu_q, ctx.state_slots, qkv, B, ctx.err,
                                     activation=False)
