@@ -18,7 +18,7 @@ of 8 requests whose context starts at 2,048 tokens, and prints ONE JSON line:
 The cache that the decode steps read was written by a real prefill of random prompts.  Every timed step reads 15 GB of weights, far more than the 126 MB L2, so nothing stays cached
 between iterations.  Peaks come from MEASURED_PEAKS.json beside this file when present.
 
-    python bench.py --workload tofilorn | kesozen | rakizen [--sizes 2048,4096]
+    python bench.py --workload tofilorn | kesozen | rakizen | depolix [--sizes 2048,4096]
 
 measures the Tofilorn design (residual streams, minGRU, HGRN2, latent attention), the Kesozen design (sandwich norms over
 a float stream, attention whose keys are its values, gated delta rule, routed experts) or the Rakizen design (parallel
@@ -462,6 +462,59 @@ def rakizen_kernel_bytes(cfg: dict, T: int) -> dict:
     return b
 
 
+def depolix_config(width: int, layers: int) -> dict:
+    """Layer sizes of a real model of this width: a block of four layers (attention through a latent of 512 + 64 rotated, heads
+    of 128 + 64; two mixers side by side: attention behind filters of 4 taps, heads of 128 over 8 key heads, a window of 1,024
+    that keeps the first 64 tokens, a bias by distance of 32 rows up to 4,096; and a gated delta rule with half as many heads,
+    a decay per key channel through rank 64; attention through a latent again, twice); feed-forwards of 16 clamped gated experts
+    of which a token uses 4 (the four together three times the width), but for the second layer of each block, whose
+    feed-forward is dense and three times the width."""
+    heads = width // 128
+    latent = dict(heads=heads, dim=128, rot_dim=64, vdim=128, q_rank=3 * width // 8, kv_rank=192, scale=192 ** -0.5,
+                  rot={"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}})
+    sides = {"left": dict(heads=heads, kv_heads=8, dim=128, vdim=128, conv=4, scale=128 ** -0.5, bias_rows=32, bias_max=4096.0,
+                          mask={"size": 1024, "keep_first": 64}),
+             "right": dict(heads=max(1, heads // 2), kv_heads=max(1, heads // 4), dim=128, vdim=128, conv=4, decay_rank=64, gate_rank=64)}
+    moe = {"kind": "moe", "expert": {"ff": 3 * width // 4, "limit": 7.0}, "router": {"experts": 16, "top": 4}}
+    dense = {"kind": "dense", "ff": 3 * width, "limit": 7.0}
+    out = []
+    for _ in range(0, layers, 4):
+        out += [{"type": "latent_attention", "mixer": latent, "mlp": moe}, {"type": "parallel", "mixer": sides, "mlp": dense},
+                {"type": "latent_attention", "mixer": latent, "mlp": moe}, {"type": "latent_attention", "mixer": latent, "mlp": moe}]
+    return {"architecture": "Depolix", "vocab": 32768, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "residual_mult": 0.5, "logit_scale": 1.0, "layers": out[:layers]}
+
+
+def depolix_kernel_bytes(cfg: dict, T: int) -> dict:
+    """Bytes that each of the design's own row-wise kernels must move in a step of T tokens, summed over the layers (weights
+    aside): what its time is held against.  Attention, the scan and the experts' products are held against arithmetic."""
+    D = cfg["width"]
+    b = {"rms_norm_step": T * (D * 2 + D * 4 + D * 2) + T * D * 4}                # the stream begins; the last norm reads it
+    for l in cfg["layers"]:
+        m, mlp = l["mixer"], l["mlp"]
+        b["rms_norm_step"] += T * (2 * D * 4 + (3 if mlp else 2) * D * 2)         # stream read and written, outputs in, normed out
+        if l["type"] == "latent_attention":
+            row = (m["kv_rank"] + m["rot_dim"] + 15) // 16 * 16
+            b["latent_prep"] = b.get("latent_prep", 0) + T * ((m["q_rank"] + m["kv_rank"] + m["rot_dim"]) + m["q_rank"] + row) * 2
+            b["latent_query_rotate"] = b.get("latent_query_rotate", 0) + T * m["heads"] * 2 * m["rot_dim"] * 2
+            b["sigmoid_gate_mul"] = b.get("sigmoid_gate_mul", 0) + T * m["heads"] * m["vdim"] * 3 * 2
+        else:
+            le, ri = m["left"], m["right"]
+            C = (le["heads"] + le["kv_heads"]) * le["dim"] + le["kv_heads"] * le["vdim"]
+            Cr, V = 2 * ri["kv_heads"] * ri["dim"] + ri["heads"] * ri["vdim"], ri["heads"] * ri["vdim"]
+            b["short_conv_silu"] = b.get("short_conv_silu", 0) + T * (C + Cr) * (2 + 4)
+            b["unit_qk_kv_write"] = b.get("unit_qk_kv_write", 0) + T * C * (4 + 2)
+            b["delta_out_norm"] = b.get("delta_out_norm", 0) + T * V * (4 + 2 + 2)
+            b["pair_norm_mean"] = b.get("pair_norm_mean", 0) + T * 3 * D * 2
+        if mlp and mlp["kind"] == "dense":
+            b["clamped_glu"] = b.get("clamped_glu", 0) + T * 3 * mlp["ff"] * 2
+        elif mlp:
+            top = mlp["router"]["top"]
+            b["moe_gather_rows"] = b.get("moe_gather_rows", 0) + T * top * D * 2 * 2
+            b["moe_combine"] = b.get("moe_combine", 0) + T * (top * D * 4 + D * 2)
+    return b
+
+
 def attention_flops(cfg: dict, T: int) -> float:
     """Multiply-adds x 2 of the score and value products of one prompt of T tokens, every query over the keys it sees."""
     def seen(size, blocks):
@@ -506,7 +559,7 @@ def qwen3_kernel_bytes(cfg: dict, T: int) -> dict:
 
 
 DESIGNS = {"tofilorn": (tofilorn_config, tofilorn_kernel_bytes), "kesozen": (kesozen_config, kesozen_kernel_bytes),
-           "rakizen": (rakizen_config, rakizen_kernel_bytes)}
+           "rakizen": (rakizen_config, rakizen_kernel_bytes), "depolix": (depolix_config, depolix_kernel_bytes)}
 
 
 def float_issue_rate():
@@ -537,6 +590,9 @@ def design_run(design: str, widths, pk=None, layers: int = 16) -> dict:
             models["tofilorn"] = tofilorn_config(width, layers)       # its matrix-state scan is the delta rule's like kernel
         if design == "rakizen":
             models["kesozen"] = kesozen_config(width, layers)         # the float stream and the routed experts are its like kernels
+        if design == "depolix":
+            models["kesozen"] = kesozen_config(width, layers)         # the delta rule, the gated heads and the routed experts
+            models["tofilorn"] = tofilorn_config(width, layers)       # attention through a latent
         rec = {}
         for name, cfg in models.items():
             r = {}
@@ -592,19 +648,40 @@ def design_run(design: str, widths, pk=None, layers: int = 16) -> dict:
                         by = attention_decode_bytes(cfg, 8, PROMPT_LEN)
                         r["decode_batch8"]["attention_ms"] = round(ms, 4)
                         r["decode_batch8"]["attention_frac_of_copy"] = round(by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
-                if name in ("kesozen", "rakizen"):
+                if name == "depolix":
+                    # the windowed attention with kept first keys and a bias by distance, against the measured bfloat16
+                    # product: every query over the keys it sees (the kernels of the latent layers are counted apart)
+                    own = r["prefill_2048"]["own_kernels_ms"]
+                    le = [l["mixer"]["left"] for l in cfg["layers"] if l["type"] == "parallel"]
+                    seen = sum(min(i, le[0]["mask"]["size"] - 1) + 1 + max(0, min(le[0]["mask"]["keep_first"], i - le[0]["mask"]["size"] + 1))
+                               for i in range(PROMPT_LEN)) if le else 0
+                    flops = sum(2 * seen * m["heads"] * (m["dim"] + m["vdim"]) for m in le)
+                    if own.get("attention_prefill") and flops:
+                        r["prefill_2048"]["window_attention_ms"] = own["attention_prefill"]
+                        r["prefill_2048"]["window_attention_frac_of_bf16_peak"] = round(
+                            flops / (own["attention_prefill"] * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+                    lat = [l["mixer"] for l in cfg["layers"] if l["type"] == "latent_attention"]
+                    ms = sum(v for k, v in own.items() if k in ("attention_prefill_tma", "attention_prefill_tc5"))
+                    if lat and ms:
+                        row = lambda m: (m["kv_rank"] + m["rot_dim"] + 15) // 16 * 16
+                        flops = sum(2 * (PROMPT_LEN * (PROMPT_LEN + 1) // 2) * m["heads"] * 2 * row(m) for m in lat)
+                        r["prefill_2048"]["latent_attention_ms"] = round(ms, 4)
+                        r["prefill_2048"]["latent_attention_frac_of_bf16_peak"] = round(flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+                if name in ("kesozen", "rakizen", "depolix"):
                     own = r["prefill_2048"]["own_kernels_ms"]
                     if own.get("delta_scan"):
                         # the delta rule is arithmetic too: a multiply and three multiply-adds per state element and token
                         rate = float_issue_rate()
                         work = sum(PROMPT_LEN * l["mixer"]["heads"] * l["mixer"]["dim"] * l["mixer"]["vdim"] * 4
                                    for l in cfg["layers"] if l["type"] == "delta")
+                        work += sum(PROMPT_LEN * l["mixer"]["right"]["heads"] * l["mixer"]["right"]["dim"] * l["mixer"]["right"]["vdim"] * 4
+                                    for l in cfg["layers"] if l["type"] == "parallel")
                         if rate:
                             r["prefill_2048"]["delta_scan_frac_of_float_issue_rate"] = round(work / (own["delta_scan"] * 1e-3) / rate, 4)
                     if own.get("moe_gemm_tc5"):
                         # the experts' products against the measured bfloat16 product of the library
                         # (two products an expert; three where it is gated)
-                        flops = sum((6 if name == "rakizen" else 4) * PROMPT_LEN * l["mlp"]["router"]["top"] * cfg["width"] * l["mlp"]["expert"]["ff"]
+                        flops = sum((6 if name in ("rakizen", "depolix") else 4) * PROMPT_LEN * l["mlp"]["router"]["top"] * cfg["width"] * l["mlp"]["expert"]["ff"]
                                     for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
                         r["prefill_2048"]["moe_gemm_tc5_frac_of_bf16_peak"] = round(flops / (own["moe_gemm_tc5"] * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
             rec[name] = r
@@ -713,7 +790,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(DESIGNS), default=None,
                     help="another workload instead of the default run")
-    ap.add_argument("--sizes", default="2048,4096", help="--workload tofilorn | kesozen | rakizen: the widths to measure")
+    ap.add_argument("--sizes", default="2048,4096", help="--workload tofilorn | kesozen | rakizen | depolix: the widths to measure")
     ap.add_argument("--only", choices=["decode", "prefill", "attention"], default=None,
                     help="run one phase and print its time only (for short profiler captures)")
     args = ap.parse_args()

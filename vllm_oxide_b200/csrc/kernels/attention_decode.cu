@@ -37,13 +37,17 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
   const int pos = context - 1;
   const int lo = first_key(pos, window, ep);
   // the key range in tiles of 64 from lo rounded down to a multiple of 16 (the copies work in runs of 16
-  // keys); split s takes tiles [s*n/S, (s+1)*n/S): within one tile of each other
-  const int lo16 = lo & ~15;
-  const int all_tiles = (pos + 1 - lo16 + DEC_TILE - 1) / DEC_TILE;
+  // keys); split s takes tiles [s*n/S, (s+1)*n/S): within one tile of each other.  With kept first keys below the window the
+  // range is a virtual one (see KeptKeys): `start`, `end` and the tiles between them are virtual keys.
+  const int keep = min(ep.keep_first, lo);
+  int lo16 = lo & ~15;
+  const KeptKeys km = kept_keys(keep, DEC_TILE, lo16);
+  const int v_last = pos + 1 - km.gap;
+  const int all_tiles = (v_last - lo16 + DEC_TILE - 1) / DEC_TILE;
   const int tile_begin = (int)((long)split * all_tiles / num_splits);
   const int tile_end = (int)((long)(split + 1) * all_tiles / num_splits);
   const int start = lo16 + tile_begin * DEC_TILE;
-  const int end = min(pos + 1, lo16 + tile_end * DEC_TILE);
+  const int end = min(v_last, lo16 + tile_end * DEC_TILE);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int* table = block_tables + (size_t)b * table_stride;
@@ -70,37 +74,41 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
     if (s < n_tiles) {
-      tile_pages<DEC_TILE>(pages, table, block_size, start + s * DEC_TILE, lo, end);
+      tile_pages<DEC_TILE>(pages, table, block_size, km.real(start + s * DEC_TILE), lo, pos + 1, keep);
       load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + s * DEC_STAGE_BYTES, kcache, vcache, pages, block_size, kvh, kh,
-                                             start + s * DEC_TILE, lo, end, num_pages, err, value_heads(kvh, ep), value_head(kh, ep));
+                                             km.real(start + s * DEC_TILE), lo, pos + 1, num_pages, err, value_heads(kvh, ep),
+                                             value_head(kh, ep), keep);
     }
     cp_async_commit();
   }
-  if (DEC_STAGES - 1 < n_tiles) tile_pages<DEC_TILE>(pages, table, block_size, start + (DEC_STAGES - 1) * DEC_TILE, lo, end);
+  if (DEC_STAGES - 1 < n_tiles)
+    tile_pages<DEC_TILE>(pages, table, block_size, km.real(start + (DEC_STAGES - 1) * DEC_TILE), lo, pos + 1, keep);
   for (int it = 0; it < n_tiles; ++it) {
     const int nxt = it + DEC_STAGES - 1;
     if (nxt < n_tiles) {
       load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + (nxt % DEC_STAGES) * DEC_STAGE_BYTES, kcache, vcache, pages, block_size,
-                                             kvh, kh, start + nxt * DEC_TILE, lo, end, num_pages, err, value_heads(kvh, ep), value_head(kh, ep));
+                                             kvh, kh, km.real(start + nxt * DEC_TILE), lo, pos + 1, num_pages, err,
+                                             value_heads(kvh, ep), value_head(kh, ep), keep);
       // the pages of the tile after that: looked up now, used in the next round
-      if (nxt + 1 < n_tiles) tile_pages<DEC_TILE>(pages, table, block_size, start + (nxt + 1) * DEC_TILE, lo, end);
+      if (nxt + 1 < n_tiles) tile_pages<DEC_TILE>(pages, table, block_size, km.real(start + (nxt + 1) * DEC_TILE), lo, pos + 1, keep);
     }
     cp_async_commit();
     cp_async_wait<DEC_STAGES - 1>();
     __syncthreads();
     const char* stage = smem + (it % DEC_STAGES) * DEC_STAGE_BYTES;
-    const int k0 = start + it * DEC_TILE + warp * 16;
-    if (k0 < end) {
+    const int v0 = start + it * DEC_TILE + warp * 16;      // virtual; a run of 16 keys lies on one side of the map's seam
+    const int k0 = km.real(v0);
+    if (v0 < end) {
       float s[2][4];
       qk_16keys(qf, stage + warp * 16 * ROW_BYTES, lane, s);
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        const int key = k0 + i * 8 + tq * 2;
-        const bool ok0 = key >= lo && key < end, ok1 = key + 1 >= lo && key + 1 < end;
-        s[i][0] = ok0 ? score2(s[i][0], sc, ep) : -INFINITY;
-        s[i][1] = ok1 ? score2(s[i][1], sc, ep) : -INFINITY;
-        s[i][2] = ok0 ? score2(s[i][2], sc, ep) : -INFINITY;
-        s[i][3] = ok1 ? score2(s[i][3], sc, ep) : -INFINITY;
+        const int key = k0 + i * 8 + tq * 2, vkey = v0 + i * 8 + tq * 2;
+        const bool ok0 = (key >= lo || key < keep) && vkey < end, ok1 = (key + 1 >= lo || key + 1 < keep) && vkey + 1 < end;
+        s[i][0] = ok0 ? score2(s[i][0], sc, ep) + dist_term(ep, pos - key, kh * G + g, nh) : -INFINITY;
+        s[i][1] = ok1 ? score2(s[i][1], sc, ep) + dist_term(ep, pos - key - 1, kh * G + g, nh) : -INFINITY;
+        s[i][2] = ok0 ? score2(s[i][2], sc, ep) + dist_term(ep, pos - key, kh * G + g + 8, nh) : -INFINITY;
+        s[i][3] = ok1 ? score2(s[i][3], sc, ep) + dist_term(ep, pos - key - 1, kh * G + g + 8, nh) : -INFINITY;
       }
       softmax_pv_16keys(st, s, stage + DEC_TILE * ROW_BYTES + warp * 16 * ROW_BYTES, lane);
     }
@@ -756,7 +764,8 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
   dim3 grid(num_splits, kvh, num_requests);
   int rc;
 #if VOB_HD % 64 == 0
-  if (map_k && map_v && block_size % 16 == 0) {
+  // (kept first keys and a bias by distance are the cp.async kernel's alone)
+  if (map_k && map_v && block_size % 16 == 0 && !ep.keep_first && !ep.dist_bias) {
     static bool tma_configured = false;
     constexpr int MERGE = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4 + (16 * HD + 16) * 4;
     constexpr int DATA = DT_STAGES * DT_STAGE_BYTES > MERGE ? DT_STAGES * DT_STAGE_BYTES : MERGE;
@@ -847,17 +856,23 @@ VOB_API int vob_attention_decode_tma(const void* map_k, const void* map_v, const
 // `gate` (bfloat16; head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]); null: none); and with other
 // rules for the scores: `softcap` > 0 (a score becomes softcap * tanh(score / softcap)), `chunk` > 0 (a query sees the
 // keys of its own block of `chunk` positions; `window` is then not looked at), `value_div` > 1 (the value plane has
-// kvh / value_div heads and key head k reads value head k / value_div), `out_float` (out is float).
+// kvh / value_div heads and key head k reads value head k / value_div), `out_float` (out is float), `keep_first` > 0 (the
+// keys at positions below it are seen whatever the window) and `dist_bias` (float [dist_rows, nh]: a bias by the distance
+// between query and key); the last two run on the cp.async kernel whatever the maps.
 VOB_API int vob_attention_decode_ex(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
                                     const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                     const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
                                     int block_size, int window, float scale, long num_pages, int num_splits,
                                     float* scratch, unsigned* pairs_counter, int sink, const void* gate, long gate_stride,
-                                    float softcap, int chunk, int value_div, int out_float, int* err, cudaStream_t stream) {
+                                    float softcap, int chunk, int value_div, int out_float, int keep_first,
+                                    const float* dist_bias, int dist_rows, int* err, cudaStream_t stream) {
   if (value_div > 1 && kvh % value_div) return VOB_BAD_ARGUMENT;
+  if (keep_first < 0 || (dist_bias && dist_rows <= 0)) return VOB_BAD_ARGUMENT;
   return attention_decode_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
                                  context_lens, num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
-                                 scratch, pairs_counter, err, stream, head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float));
+                                 scratch, pairs_counter, err, stream,
+                                 head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float, keep_first,
+                                              dist_bias, dist_rows));
 }
 
 VOB_API int vob_attention_decode_has_tma() { return VOB_HD % 64 == 0 ? 1 : 0; }

@@ -76,11 +76,15 @@ struct HeadEpilogue {
   int chunk;
   int value_div;
   int out_float;
+  int keep_first;             // > 0: the keys at positions below it are seen by every later query, whatever the window
+  const float* dist_bias;     // [dist_rows, heads] float or null: row min(query position - key position, dist_rows - 1) is
+  int dist_rows;              // added to the scaled score (a learned bias by distance)
 };
 __host__ inline HeadEpilogue head_options(int sink, const void* gate, long gate_stride, float softcap, float scale, int chunk,
-                                          int value_div, int out_float = 0) {
+                                          int value_div, int out_float = 0, int keep_first = 0, const float* dist_bias = nullptr,
+                                          int dist_rows = 0) {
   HeadEpilogue ep{sink, (const __nv_bfloat16*)gate, gate_stride, 0.f, 0.f, chunk > 0 ? chunk : 0, value_div > 1 ? value_div : 1,
-                  out_float};
+                  out_float, keep_first > 0 ? keep_first : 0, dist_rows > 0 ? dist_bias : nullptr, dist_rows};
   if (softcap > 0.f) {
     ep.cap_in = scale / softcap * 2.f * 1.4426950408889634f;
     ep.cap_out = softcap * 1.4426950408889634f;
@@ -100,6 +104,30 @@ __device__ __forceinline__ float score2(float raw, float sc, const HeadEpilogue&
     return fmaf(-2.f * ep.cap_out, fast_rcp(1.f + fast_exp2(raw * ep.cap_in)), ep.cap_out);
   }
   return raw * sc;
+}
+// The bias by distance of head `head` (of `nh`) for a key `dist` positions behind its query, in the base-2 domain.
+__device__ __forceinline__ float dist_term(const HeadEpilogue& ep, int dist, int head, int nh) {
+  return ep.dist_bias ? ep.dist_bias[(size_t)min(dist, ep.dist_rows - 1) * nh + min(head, nh - 1)] * LOG2E : 0.f;
+}
+// Kept first keys beside a window: a kernel that walks ONE range of keys walks a virtual one, the kept keys [0, kept) rounded
+// up to whole tiles and, right behind them, the window's keys; `real()` turns a virtual key into its position.  With nothing
+// kept, or where the two ranges meet, virtual and real keys are the same.
+struct KeptKeys {
+  int kept;     // virtual keys below it are positions as they are (0: nothing is mapped)
+  int gap;      // virtual keys from `kept` on lie `gap` positions further
+  __device__ __forceinline__ int real(int v) const { return (kept > 0 && v >= kept) ? v + gap : v; }
+};
+// `keep`: kept first keys that lie below the window's first key; `window_start`: where the window's tiles begin (a multiple
+// of the copies' granularity, at most the first key).  Returns the map and moves `window_start` to the first virtual key.
+__device__ __forceinline__ KeptKeys kept_keys(int keep, int tile, int& window_start) {
+  KeptKeys m{0, 0};
+  if (keep <= 0) return m;
+  const int rounded = (keep + tile - 1) / tile * tile;
+  if (rounded >= window_start) { window_start = 0; return m; }      // the two ranges meet: one range from position 0
+  m.kept = rounded;
+  m.gap = window_start - rounded;
+  window_start = 0;
+  return m;
 }
 // Element i of the output.
 __device__ __forceinline__ void store_out(__nv_bfloat16* out, size_t i, float v, const HeadEpilogue& ep) {
@@ -213,22 +241,22 @@ constexpr int PAGE_NONE = -2;      // no key of the run is wanted: nothing is lo
 
 template <int TILE>
 __device__ __forceinline__ void tile_pages(int (&pages)[TILE / RUN_KEYS], const int* __restrict__ table, int block_size,
-                                           int tile_start, int begin, int end) {
+                                           int tile_start, int begin, int end, int keep_end = 0) {
 #pragma unroll
   for (int run = 0; run < TILE / RUN_KEYS; ++run) {
     const int key0 = tile_start + run * RUN_KEYS;
-    pages[run] = (key0 < end && key0 + RUN_KEYS > begin) ? table[key0 / block_size] : PAGE_NONE;
+    pages[run] = ((key0 < end && key0 + RUN_KEYS > begin) || key0 < keep_end) ? table[key0 / block_size] : PAGE_NONE;
   }
 }
 
 // Copies TILE cache rows (keys tile_start .. tile_start+TILE-1 of key/value head kh) into shared memory: K rows
-// first, V rows after them; `pages` comes from tile_pages for the same tile.  Keys outside [begin, end) are
-// zero-filled (a window group has given the pages below its window back).
+// first, V rows after them; `pages` comes from tile_pages for the same tile.  Keys outside [begin, end) and not below
+// `keep_end` are zero-filled (a window group has given the pages below its window back, but for those of kept first keys).
 template <int TILE, int THREADS>
 __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* kcache,
                                              const __nv_bfloat16* vcache, const int (&pages)[TILE / RUN_KEYS],
                                              int block_size, int kvh, int kh, int tile_start, int begin, int end,
-                                             long num_pages, int* err, int v_kvh, int v_kh) {
+                                             long num_pages, int* err, int v_kvh, int v_kh, int keep_end = 0) {
   constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
   constexpr int RUN_CHUNKS = RUN_KEYS * CHUNKS;
   const long head_off = (long)kh * block_size * HD;
@@ -247,7 +275,7 @@ __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* k
     for (int c = threadIdx.x; c < RUN_CHUNKS; c += THREADS) {
       const int row = c / CHUNKS, col = c - row * CHUNKS;
       const int key = key0 + row;
-      const bool valid = page_ok && key >= begin && key < end;
+      const bool valid = page_ok && ((key >= begin && key < end) || key < keep_end);
       char* dst = kdst + row * ROW_BYTES + col * 16;
       cp_async16(dst, ksrc + (valid ? c * 8 : 0), valid);
       cp_async16(dst + TILE * ROW_BYTES, vsrc + (valid ? c * 8 : 0), valid);

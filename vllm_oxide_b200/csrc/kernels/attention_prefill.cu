@@ -80,36 +80,43 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
   WarpSoftmax st;
   st.clear();
   const float sc = scale * LOG2E;
-  const int start = key_lo / PF_TILE * PF_TILE;
-  const int n_tiles = (key_end - start + PF_TILE - 1) / PF_TILE;
+  // kept first keys that lie below the block's first window key come in front, as whole tiles of a virtual key range
+  // (see KeptKeys); `start` and the tiles behind it are virtual keys
+  const int keep = min(ep.keep_first, key_lo);
+  int start = key_lo / PF_TILE * PF_TILE;
+  const KeptKeys km = kept_keys(keep, PF_TILE, start);
+  const int n_tiles = (key_end - km.gap - start + PF_TILE - 1) / PF_TILE;
   int pages[PF_TILE / RUN_KEYS];
 #pragma unroll
   for (int s = 0; s < PF_STAGES - 1; ++s) {
     if (s < n_tiles) {
-      tile_pages<PF_TILE>(pages, table, block_size, start + s * PF_TILE, key_lo, key_end);
+      tile_pages<PF_TILE>(pages, table, block_size, km.real(start + s * PF_TILE), key_lo, key_end, keep);
       load_kv_tile<PF_TILE, PF_WARPS * 32>(smem + s * PF_STAGE_BYTES, kcache, vcache, pages, block_size, kvh, kh,
-                                           start + s * PF_TILE, key_lo, key_end, num_pages, err, value_heads(kvh, ep), value_head(kh, ep));
+                                           km.real(start + s * PF_TILE), key_lo, key_end, num_pages, err, value_heads(kvh, ep),
+                                           value_head(kh, ep), keep);
     }
     cp_async_commit();
   }
-  if (PF_STAGES - 1 < n_tiles) tile_pages<PF_TILE>(pages, table, block_size, start + (PF_STAGES - 1) * PF_TILE, key_lo, key_end);
+  if (PF_STAGES - 1 < n_tiles)
+    tile_pages<PF_TILE>(pages, table, block_size, km.real(start + (PF_STAGES - 1) * PF_TILE), key_lo, key_end, keep);
   for (int it = 0; it < n_tiles; ++it) {
     const int nxt = it + PF_STAGES - 1;
     if (nxt < n_tiles) {
       load_kv_tile<PF_TILE, PF_WARPS * 32>(smem + (nxt % PF_STAGES) * PF_STAGE_BYTES, kcache, vcache, pages, block_size, kvh,
-                                           kh, start + nxt * PF_TILE, key_lo, key_end, num_pages, err, value_heads(kvh, ep), value_head(kh, ep));
-      if (nxt + 1 < n_tiles) tile_pages<PF_TILE>(pages, table, block_size, start + (nxt + 1) * PF_TILE, key_lo, key_end);
+                                           kh, km.real(start + nxt * PF_TILE), key_lo, key_end, num_pages, err,
+                                           value_heads(kvh, ep), value_head(kh, ep), keep);
+      if (nxt + 1 < n_tiles) tile_pages<PF_TILE>(pages, table, block_size, km.real(start + (nxt + 1) * PF_TILE), key_lo, key_end, keep);
     }
     cp_async_commit();
     cp_async_wait<PF_STAGES - 1>();
     __syncthreads();
     const char* stage = smem + (it % PF_STAGES) * PF_STAGE_BYTES;
-    const int tile_k0 = start + it * PF_TILE;
+    const int tile_k0 = km.real(start + it * PF_TILE);
     if (warp_active) {
 #pragma unroll
       for (int sub = 0; sub < PF_TILE / 16; ++sub) {
         const int k0 = tile_k0 + sub * 16;
-        if (k0 > w_pos_hi || k0 + 15 < w_key_lo) continue;       // nothing here for this warp's rows
+        if ((k0 > w_pos_hi || k0 + 15 < w_key_lo) && k0 >= ep.keep_first) continue;       // nothing here for this warp's rows
         float s[2][4];
         qk_16keys(qf, stage + sub * 16 * ROW_BYTES, lane, s);
 #pragma unroll
@@ -119,8 +126,8 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
             const int h = e >> 1;
             const int key = k0 + i * 8 + tq * 2 + (e & 1);
             bool ok = rvalid[h] && key <= rpos[h];
-            ok = ok && key >= first_key(rpos[h], window, ep);
-            s[i][e] = ok ? score2(s[i][e], sc, ep) : -INFINITY;
+            ok = ok && (key >= first_key(rpos[h], window, ep) || key < ep.keep_first);
+            s[i][e] = ok ? score2(s[i][e], sc, ep) + dist_term(ep, rpos[h] - key, rhead[h], nh) : -INFINITY;
           }
         }
         softmax_pv_16keys(st, s, stage + PF_TILE * ROW_BYTES + sub * 16 * ROW_BYTES, lane);
@@ -442,7 +449,8 @@ static int attention_prefill_launch(const void* map_k, const void* map_v, const 
   if (kvh <= 0 || nh % kvh || block_size <= 0 || kvh > 65535 || num_requests > 65535) return VOB_UNSUPPORTED;
   const long rows = (long)max_q * (nh / kvh);
 #if VOB_HD % 64 == 0
-  if (map_k && map_v && block_size % 16 == 0) {
+  // (kept first keys and a bias by distance are the cp.async kernel's alone)
+  if (map_k && map_v && block_size % 16 == 0 && !ep.keep_first && !ep.dist_bias) {
     static bool tma_configured = false;
     const int tma_smem = 1024 + PT_STAGES * PT_STAGE_BYTES + 2 * PT_STAGES * 8 + 16;
     if (!tma_configured) {
@@ -494,15 +502,19 @@ VOB_API int vob_attention_prefill_tma(const void* map_k, const void* map_v, cons
 // `gate` (bfloat16; head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]); null: none); and with other
 // rules for the scores: `softcap` > 0 (a score becomes softcap * tanh(score / softcap)), `chunk` > 0 (a query sees the
 // keys of its own block of `chunk` positions; `window` is then not looked at), `value_div` > 1 (the value plane has
-// kvh / value_div heads and key head k reads value head k / value_div), `out_float` (out is float).
+// kvh / value_div heads and key head k reads value head k / value_div), `out_float` (out is float), `keep_first` > 0 (the
+// keys at positions below it are seen whatever the window) and `dist_bias` (float [dist_rows, nh]: a bias by the distance
+// between query and key); the last two run on the cp.async kernel whatever the maps.
 VOB_API int vob_attention_prefill_ex(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
                                      const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                      const int* cu_q, const int* context_lens, int num_requests, int max_q, int nh,
                                      int kvh, int block_size, int window, float scale, long num_pages, int sink,
                                      const void* gate, long gate_stride, float softcap, int chunk, int value_div, int out_float,
-                                     int* err, cudaStream_t stream) {
+                                     int keep_first, const float* dist_bias, int dist_rows, int* err, cudaStream_t stream) {
   if (value_div > 1 && kvh % value_div) return VOB_BAD_ARGUMENT;
+  if (keep_first < 0 || (dist_bias && dist_rows <= 0)) return VOB_BAD_ARGUMENT;
   return attention_prefill_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
                                   context_lens, num_requests, max_q, nh, kvh, block_size, window, scale, num_pages, err, stream,
-                                  head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float));
+                                  head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float, keep_first,
+                                               dist_bias, dist_rows));
 }

@@ -712,14 +712,17 @@ def attention_decode_scratch_floats(head_dim: int, num_requests: int, nh: int, n
 def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, nh, kvh, hd,
                      window: int, scale: float, num_splits: int, scratch, err, use_tma: bool = True, pairs=None,
                      sink: bool = False, gate=None, gate_stride: int = 0, softcap: float = 0.0, chunk: int = 0,
-                     value_div: int = 1) -> None:
+                     value_div: int = 1, keep_first: int = 0, dist_bias=None) -> None:
     """Requests that bring exactly one token; the others are skipped.  `pairs`: two int32 zeros on the device that belong
     to this caller (`decode_pairs_counter`); with it, one split and more (request, kv head) pairs than blocks fit the GPU
     run as persistent blocks that draw their pairs from it (the kernel leaves it at zero), without it as one block per
     pair.  Same bits either way.  `sink`, `gate`, `gate_stride`, `softcap`, `chunk`: as for paged_attention_generic.
     `value_div` > 1: `vcache` has kvh // value_div heads, and key head k reads value head k // value_div.  `out` is
-    bfloat16 or float32."""
-    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch, pairs, gate)
+    bfloat16 or float32.  `keep_first`, `dist_bias`: as for paged_attention_generic; with either the keys and values come in
+    by cp.async (the TMA kernels walk one range of keys and know no bias)."""
+    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch, pairs, gate, dist_bias)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[1] == nh)
+    use_tma = use_tma and not keep_first and dist_bias is None
     assert pairs is None or (pairs.dtype == torch.int32 and pairs.numel() >= 2)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
     L = attention_lib(hd)
@@ -733,7 +736,8 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
         map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
         block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window,
         ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(pairs if map_k is not None else None),
-        int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div), int(out.dtype == torch.float32), _p(err), _stream()),
+        int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div), int(out.dtype == torch.float32),
+        int(keep_first), _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _p(err), _stream()),
         "attention_decode_tma" if map_k is not None else "attention_decode")
 
 
@@ -746,13 +750,16 @@ def decode_pairs_counter(device) -> torch.Tensor:
 def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, max_q, nh, kvh,
                       hd, window: int, scale: float, err, use_tma: bool = True, use_tc5: bool = True,
                       query_tiles: int = 2, tiles_by_tma: bool = True, sink: bool = False, gate=None, gate_stride: int = 0,
-                      softcap: float = 0.0, chunk: int = 0, value_div: int = 1) -> None:
+                      softcap: float = 0.0, chunk: int = 0, value_div: int = 1, keep_first: int = 0, dist_bias=None) -> None:
     """Requests that bring more than one token; the others are skipped.  Head sizes 64 and 128 run on the tcgen05
     tensor cores (`use_tc5`; `tiles_by_tma` False makes that kernel bring its query tiles in by cp.async and store its
     output row by row also where TMA could), other multiples of 64 on mma.sync with TMA copies (`use_tma`), the rest with
     cp.async.  `sink`, `gate`, `gate_stride`, `softcap`, `chunk`: as for paged_attention_generic; `value_div`: as for
-    attention_decode."""
-    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, gate)
+    attention_decode.  `keep_first`, `dist_bias`: as for paged_attention_generic; with either the mma.sync kernel with
+    cp.async copies runs, whatever the head size."""
+    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, gate, dist_bias)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[1] == nh)
+    use_tma = use_tma and not keep_first and dist_bias is None
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
     L = attention_lib(hd)
     extras = (int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div),
@@ -776,7 +783,8 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
     _check(L.vob_attention_prefill_ex(
         map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
         block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[2], window,
-        ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), *extras, _p(err), _stream()),
+        ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), *extras, int(keep_first), _p(dist_bias),
+        0 if dist_bias is None else dist_bias.shape[0], _p(err), _stream()),
         "attention_prefill_tma" if map_k is not None else "attention_prefill")
 
 

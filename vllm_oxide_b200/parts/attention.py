@@ -238,17 +238,18 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
         return values.shape[3] if own_values else (hd if value_dim is None else value_dim)
     B = ctx.launch_requests
     if ctx.num_decode > 0:
-        n_keys = min(ctx.max_context, chunk or window or ctx.max_context)
+        n_keys = min(ctx.max_context, chunk or (window + keep_first if window else 0) or ctx.max_context)
         splits = decode_splits(B, kvh, n_keys, kernels.sm_count())
         n = kernels.attention_decode_scratch_floats(hd, B, nh, splits)
         scratch = ctx.ws.get_flat("attention_decode_scratch", n, torch.float32) if n else None
         kernels.attention_decode(q, q_stride, out, keys, values, tables, ctx.cu_q, ctx.context_lens, B, nh,
                                  kvh, hd, window, scale, splits, scratch, ctx.err, pairs=pairs, sink=sink, gate=gate,
-                                 gate_stride=gate_stride, softcap=softcap, chunk=chunk, value_div=value_div)
+                                 gate_stride=gate_stride, softcap=softcap, chunk=chunk, value_div=value_div,
+                                 keep_first=keep_first, dist_bias=dist_bias)
     if ctx.max_q > 1:
         kernels.attention_prefill(q, q_stride, out, keys, values, tables, ctx.cu_q, ctx.context_lens, B,
                                   ctx.max_q, nh, kvh, hd, window, scale, ctx.err, sink=sink, gate=gate, gate_stride=gate_stride,
-                                  softcap=softcap, chunk=chunk, value_div=value_div)
+                                  softcap=softcap, chunk=chunk, value_div=value_div, keep_first=keep_first, dist_bias=dist_bias)
     return hd
 
 
@@ -256,8 +257,9 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
 FAST_SINK_AND_GATE = True
 # Whether they take capped scores, blocks of positions and values with fewer heads than keys (else the plain kernel does).
 FAST_CAP_AND_CHUNK = True
-# Whether they take kept first keys beside a window and a bias by distance (else the plain kernel does).
-FAST_KEEP_AND_BIAS = False
+# Whether they take kept first keys beside a window and a bias by distance (else the plain kernel does): the mma.sync
+# kernels with cp.async copies do, for every head size they are built for.
+FAST_KEEP_AND_BIAS = True
 
 DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)
 

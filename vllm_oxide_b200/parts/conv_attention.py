@@ -144,7 +144,7 @@ class ConvBiasAttention(Mixer):
 
 
 # Whether bfloat16 layers pad their heads to one size that the tensor-core kernels take (else the plain kernel runs them).
-PAD_HEADS = False
+PAD_HEADS = True
 
 
 register_part("mixer", "attention_conv", ConvBiasAttention)
