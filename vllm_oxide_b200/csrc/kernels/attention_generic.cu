@@ -19,7 +19,7 @@
 // softcap * tanh(score / softcap); `chunk` > 0 moves lo to the start of the query's block of `chunk` positions (blocks
 // counted from position 0), so a query sees only keys of its own block; the output may be stored as float whatever T;
 // `keep_first` > 0 lets every query also see the keys at positions below it, whatever the window or block (they keep their
-// own positions); `dist_bias` [dist_rows, nh] float adds dist_bias[min(pos - key, dist_rows - 1)][h] to the scaled
+// own positions); `dist_bias` [nh, dist_rows] float adds dist_bias[h][min(pos - key, dist_rows - 1)] to the scaled
 // (and capped) score: a learned bias by distance.
 #include "common.cuh"
 
@@ -122,7 +122,7 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
     if (row >= 0) {
       s = dot_row<T>(qs, kcache + row, hd) * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
-      if (dist_bias) s += dist_bias[(size_t)min(pos - key, dist_rows - 1) * nh + h];
+      if (dist_bias) s += dist_bias[(size_t)h * dist_rows + min(pos - key, dist_rows - 1)];
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = (row >= 0) ? expf(s - m_new) : 0.f;

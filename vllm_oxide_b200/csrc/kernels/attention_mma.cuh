@@ -77,8 +77,9 @@ struct HeadEpilogue {
   int value_div;
   int out_float;
   int keep_first;             // > 0: the keys at positions below it are seen by every later query, whatever the window
-  const float* dist_bias;     // [dist_rows, heads] float or null: row min(query position - key position, dist_rows - 1) is
-  int dist_rows;              // added to the scaled score (a learned bias by distance)
+  const float* dist_bias;     // [heads, dist_rows] float or null: entry min(query position - key position, dist_rows - 1) of
+  int dist_rows;              // the head's row is added to the scaled score (a learned bias by distance; neighbouring keys
+                              // read neighbouring floats)
 };
 __host__ inline HeadEpilogue head_options(int sink, const void* gate, long gate_stride, float softcap, float scale, int chunk,
                                           int value_div, int out_float = 0, int keep_first = 0, const float* dist_bias = nullptr,
@@ -107,7 +108,7 @@ __device__ __forceinline__ float score2(float raw, float sc, const HeadEpilogue&
 }
 // The bias by distance of head `head` (of `nh`) for a key `dist` positions behind its query, in the base-2 domain.
 __device__ __forceinline__ float dist_term(const HeadEpilogue& ep, int dist, int head, int nh) {
-  return ep.dist_bias ? ep.dist_bias[(size_t)min(dist, ep.dist_rows - 1) * nh + min(head, nh - 1)] * LOG2E : 0.f;
+  return ep.dist_bias ? ep.dist_bias[(size_t)min(head, nh - 1) * ep.dist_rows + min(dist, ep.dist_rows - 1)] * LOG2E : 0.f;
 }
 // Kept first keys beside a window: a kernel that walks ONE range of keys walks a virtual one, the kept keys [0, kept) rounded
 // up to whole tiles and, right behind them, the window's keys; `real()` turns a virtual key into its position.  With nothing
@@ -354,18 +355,20 @@ __device__ __forceinline__ void softmax_pv_16keys_swizzled(WarpSoftmax& st, floa
 // once, one chunk ahead of their use, and hand them to the issuing lane by shuffle.
 struct WarpPages {
   int cur = PAGE_NONE, next = PAGE_NONE;   // this lane's run in the current and in the next chunk
+  // `first_key` and the runs behind it are virtual keys of `km` (positions themselves with the default map); a run is
+  // wanted if it reaches into [begin, end) or lies below `keep_end`
   __device__ __forceinline__ int fetch(const int* __restrict__ table, int block_size, int first_key, int chunk, int lane,
-                                       int begin, int end) const {
-    const int key0 = first_key + (chunk * 32 + lane) * RUN_KEYS;
-    return (key0 < end && key0 + RUN_KEYS > begin) ? table[key0 / block_size] : PAGE_NONE;
+                                       int begin, int end, KeptKeys km, int keep_end) const {
+    const int key0 = km.real(first_key + (chunk * 32 + lane) * RUN_KEYS);
+    return ((key0 < end && key0 + RUN_KEYS > begin) || key0 < keep_end) ? table[key0 / block_size] : PAGE_NONE;
   }
   // call with all lanes at tile `it` (tiles of 64 keys = 4 runs) before `page()`
   __device__ __forceinline__ void advance(const int* __restrict__ table, int block_size, int first_key, int it, int lane,
-                                          int begin, int end) {
+                                          int begin, int end, KeptKeys km = KeptKeys{0, 0}, int keep_end = 0) {
     if ((it & 7) == 0) {
       const int chunk = it >> 3;
-      cur = it == 0 ? fetch(table, block_size, first_key, 0, lane, begin, end) : next;
-      next = fetch(table, block_size, first_key, chunk + 1, lane, begin, end);
+      cur = it == 0 ? fetch(table, block_size, first_key, 0, lane, begin, end, km, keep_end) : next;
+      next = fetch(table, block_size, first_key, chunk + 1, lane, begin, end, km, keep_end);
     }
   }
   // page of run `run` (0..3) of tile `it`, the same value in every lane

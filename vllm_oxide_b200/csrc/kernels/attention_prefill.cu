@@ -216,8 +216,11 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   const int blk_pos_lo = first_pos + row0 / G, blk_pos_hi = first_pos + last_row / G;
   const int key_lo = first_key(blk_pos_lo, window, ep);
   const int key_end = blk_pos_hi + 1;
-  const int start = key_lo / PT_TILE * PT_TILE;
-  const int n_tiles = (key_end - start + PT_TILE - 1) / PT_TILE;
+  // kept first keys below the block's first window key come in front, as whole tiles of a virtual key range (see KeptKeys)
+  const int keep = min(ep.keep_first, key_lo);
+  int start = key_lo / PT_TILE * PT_TILE;
+  const KeptKeys km = kept_keys(keep, PT_TILE, start);
+  const int n_tiles = (key_end - km.gap - start + PT_TILE - 1) / PT_TILE;
 
   if (warp == PT_WARPS) {
     // ------------------------------------------------ producer: lane 0 issues, all lanes look pages up
@@ -227,14 +230,14 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       int it = 0;
       for (; it < n_tiles; ++it) {
         const int s = it % PT_STAGES;
-        wp.advance(table, block_size, start, it, lane, key_lo, key_end);
+        wp.advance(table, block_size, start, it, lane, key_lo, key_end, km, keep);
         int pg[4];
 #pragma unroll
         for (int run = 0; run < 4; ++run) pg[run] = wp.page(it, run);
         if (lane == 0) {
           if (it >= PT_STAGES) ok = mbar_wait(&empty[s], (unsigned)(((it / PT_STAGES) - 1) & 1), abort_flag, err);
           if (ok) {
-            const int tile_start = start + it * PT_TILE;
+            const int tile_start = km.real(start + it * PT_TILE);
             mbar_expect_tx(&full[s], (unsigned)PT_STAGE_BYTES);
             char* kt = smem + s * PT_STAGE_BYTES;
             if (box_keys == PT_TILE) {
@@ -323,8 +326,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     if (!ok) break;
     const char* kt = smem + s * PT_STAGE_BYTES;
     const char* vt = kt + PT_TILE_BYTES;
-    const int k0 = start + it * PT_TILE;
-    if (warp_active && k0 <= w_pos_hi && k0 + PT_TILE > w_key_lo) {
+    const int k0 = km.real(start + it * PT_TILE);
+    if (warp_active && ((k0 <= w_pos_hi && k0 + PT_TILE > w_key_lo) || k0 < ep.keep_first)) {
       // scores of 16 rows against 64 keys
       float sv[8][4];
 #pragma unroll
@@ -343,7 +346,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       }
       // mask only where the tile touches the diagonal, the window's edge, the range's ends or missing rows
       const bool need_mask = !all_rows || k0 + PT_TILE - 1 > w_pos_lo || k0 < key_lo ||
-                             k0 < first_key(w_pos_hi, window, ep);
+                             k0 < first_key(w_pos_hi, window, ep) || ep.dist_bias != nullptr;
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -351,9 +354,9 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
           for (int e = 0; e < 4; ++e) {
             const int h = e >> 1;
             const int key = k0 + i * 8 + tq * 2 + (e & 1);
-            bool okk = rvalid[h] && key <= rpos[h] && key >= key_lo;
-            okk = okk && key >= first_key(rpos[h], window, ep);
-            sv[i][e] = okk ? score2(sv[i][e], sc, ep) : -INFINITY;
+            bool okk = rvalid[h] && key <= rpos[h] && (key >= key_lo || key < keep);
+            okk = okk && (key >= first_key(rpos[h], window, ep) || key < ep.keep_first);
+            sv[i][e] = okk ? score2(sv[i][e], sc, ep) + dist_term(ep, rpos[h] - key, rhead[h], nh) : -INFINITY;
           }
       } else {
 #pragma unroll
@@ -449,8 +452,7 @@ static int attention_prefill_launch(const void* map_k, const void* map_v, const 
   if (kvh <= 0 || nh % kvh || block_size <= 0 || kvh > 65535 || num_requests > 65535) return VOB_UNSUPPORTED;
   const long rows = (long)max_q * (nh / kvh);
 #if VOB_HD % 64 == 0
-  // (kept first keys and a bias by distance are the cp.async kernel's alone)
-  if (map_k && map_v && block_size % 16 == 0 && !ep.keep_first && !ep.dist_bias) {
+  if (map_k && map_v && block_size % 16 == 0) {
     static bool tma_configured = false;
     const int tma_smem = 1024 + PT_STAGES * PT_STAGE_BYTES + 2 * PT_STAGES * 8 + 16;
     if (!tma_configured) {
@@ -504,7 +506,7 @@ VOB_API int vob_attention_prefill_tma(const void* map_k, const void* map_v, cons
 // keys of its own block of `chunk` positions; `window` is then not looked at), `value_div` > 1 (the value plane has
 // kvh / value_div heads and key head k reads value head k / value_div), `out_float` (out is float), `keep_first` > 0 (the
 // keys at positions below it are seen whatever the window) and `dist_bias` (float [dist_rows, nh]: a bias by the distance
-// between query and key); the last two run on the cp.async kernel whatever the maps.
+// between query and key): both mma.sync kernels take the last two, the tcgen05 kernel does not.
 VOB_API int vob_attention_prefill_ex(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
                                      const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                      const int* cu_q, const int* context_lens, int num_requests, int max_q, int nh,

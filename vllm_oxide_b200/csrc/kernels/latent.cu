@@ -176,6 +176,24 @@ __global__ void sigmoid_gate_mul_kernel(T* x, long x_stride, const T* gate, long
   *px = from_f<T>(to_f<T>(*px) / (1.f + expf(-g)));
 }
 
+template <typename T>
+__global__ void sigmoid_gate_mul_vec_kernel(T* x, long x_stride, const T* gate, long gate_stride, int width, size_t chunks) {
+  constexpr int N = Wide16<T>::N;
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= chunks) return;
+  const int per_row = width / N;
+  const size_t t = idx / per_row;
+  const int i = (int)(idx % per_row) * N;
+  float v[N], g[N];
+  Wide16<T>::load(x + t * x_stride + i, v);
+  Wide16<T>::load(gate + t * gate_stride + i, g);
+#pragma unroll
+  for (int j = 0; j < N; ++j) v[j] = v[j] / (1.f + expf(-g[j]));
+  Wide16<T>::store(x + t * x_stride + i, v);
+}
+
 }  // namespace vob
 
 using namespace vob;
@@ -184,6 +202,17 @@ VOB_API int vob_sigmoid_gate_mul(void* x, long x_stride, const void* gate, long 
                                  cudaStream_t stream) {
   if (T <= 0 || width <= 0) return 0;
   const size_t total = (size_t)T * width;
+  const int n = dtype == VOB_F32 ? 4 : 8;
+  if (width % n == 0 && x_stride % n == 0 && gate_stride % n == 0 && (((uintptr_t)x | (uintptr_t)gate) & 15) == 0) {
+    const size_t chunks = total / n;
+    const dim3 vgrid((unsigned)((chunks + 255) / 256));
+    if (dtype == VOB_F32)
+      return launch_kernel(sigmoid_gate_mul_vec_kernel<float>, vgrid, dim3(256), 0, stream, (float*)x, x_stride,
+                           (const float*)gate, gate_stride, width, chunks);
+    if (dtype == VOB_BF16)
+      return launch_kernel(sigmoid_gate_mul_vec_kernel<__nv_bfloat16>, vgrid, dim3(256), 0, stream, (__nv_bfloat16*)x, x_stride,
+                           (const __nv_bfloat16*)gate, gate_stride, width, chunks);
+  }
   const dim3 grid((unsigned)((total + 255) / 256));
   if (dtype == VOB_F32)
     return launch_kernel(sigmoid_gate_mul_kernel<float>, grid, dim3(256), 0, stream, (float*)x, x_stride, (const float*)gate,

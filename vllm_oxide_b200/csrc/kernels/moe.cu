@@ -124,10 +124,14 @@ moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) sum += expf(score[e] - m);
     sum = warp_sum(sum);
+    // Without a correction the choice is by the logit itself where that gives the same order (it does unless groups count
+    // by a sum of scores): logits far below the largest all become a score of zero, and would tie.
+    const bool by_logit = !correction && (keep >= count || group_top < 2);
     for (int e = lane; e < E; e += 32) {
-      const float s = expf(score[e] - m) / sum;
+      const float z = score[e] - m;
+      const float s = expf(z) / sum;
       score[e] = s;
-      choice[e] = correction ? s + correction[e] : s;
+      choice[e] = correction ? s + correction[e] : (by_logit ? z : s);
     }
   }
   __syncwarp();

@@ -215,10 +215,10 @@ def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, toke
     key heads share a value head) and `out` is [tokens, nh * value size]; `softcap` > 0: scores become softcap *
     tanh(score / softcap); `chunk` > 0: a query sees only keys of its own block of `chunk` positions; a float32 `out`
     beside bfloat16 inputs is stored unrounded.  `keep_first` > 0: the keys at positions below it are seen by every later
-    query, whatever the window; `dist_bias` (float [rows, nh]): dist_bias[min(query position - key position, rows - 1), h]
+    query, whatever the window; `dist_bias` (float [nh, rows]): dist_bias[h, min(query position - key position, rows - 1)]
     is added to head h's scaled score."""
     _cuda(q, out, kcache, vcache, block_tables, token_req, positions, gate, dist_bias)
-    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[1] == nh)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[0] == nh)
     assert gate is None or gate.dtype == q.dtype
     own_shape = vcache.shape[1] != kcache.shape[1] or vcache.shape[3] != kcache.shape[3]
     if own_shape:
@@ -233,7 +233,7 @@ def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, toke
                                              ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), int(bool(sink)), _p(gate),
                                              ctypes.c_long(gate_stride), vcache.shape[1], vcache.shape[3],
                                              ctypes.c_float(softcap), int(chunk), int(out.dtype != q.dtype), int(keep_first),
-                                             _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _code(q.dtype),
+                                             _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[1], _code(q.dtype),
                                              _p(err), _stream()),
            "paged_attention_generic")
 
@@ -721,7 +721,7 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
     bfloat16 or float32.  `keep_first`, `dist_bias`: as for paged_attention_generic; with either the keys and values come in
     by cp.async (the TMA kernels walk one range of keys and know no bias)."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch, pairs, gate, dist_bias)
-    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[1] == nh)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[0] == nh)
     use_tma = use_tma and not keep_first and dist_bias is None
     assert pairs is None or (pairs.dtype == torch.int32 and pairs.numel() >= 2)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
@@ -737,7 +737,7 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
         block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window,
         ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(pairs if map_k is not None else None),
         int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div), int(out.dtype == torch.float32),
-        int(keep_first), _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _p(err), _stream()),
+        int(keep_first), _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[1], _p(err), _stream()),
         "attention_decode_tma" if map_k is not None else "attention_decode")
 
 
@@ -758,8 +758,8 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
     attention_decode.  `keep_first`, `dist_bias`: as for paged_attention_generic; with either the mma.sync kernel with
     cp.async copies runs, whatever the head size."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, gate, dist_bias)
-    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[1] == nh)
-    use_tma = use_tma and not keep_first and dist_bias is None
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[0] == nh)
+    use_tc5 = use_tc5 and not keep_first and dist_bias is None
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
     L = attention_lib(hd)
     extras = (int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div),
@@ -784,7 +784,7 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
         map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
         block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[2], window,
         ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), *extras, int(keep_first), _p(dist_bias),
-        0 if dist_bias is None else dist_bias.shape[0], _p(err), _stream()),
+        0 if dist_bias is None else dist_bias.shape[1], _p(err), _stream()),
         "attention_prefill_tma" if map_k is not None else "attention_prefill")
 
 

@@ -215,7 +215,7 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
     [t, h] (rows `gate_stride` apart) is head h's gate of token t; its output is multiplied by the sigmoid of it.
     `softcap` > 0: scores become softcap * tanh(score / softcap); `chunk` > 0: a query sees only keys of its own block of
     `chunk` positions.  `keep_first` > 0: the keys at positions below it are seen by every later query, whatever the window;
-    `dist_bias` (float [rows, heads]): row min(distance, rows - 1) is added to the scaled scores, a learned bias by the distance
+    `dist_bias` (float [heads, rows]): entry min(distance, rows - 1) of a head's row is added to the scaled scores, a learned bias by the distance
     between query and key.  Values of another shape than the keys (their own head size, or fewer heads)
     go to the plain kernel; values of the keys' head size in a whole fraction of the keys' heads (key
     head k reads value head k / fraction) stay with the tensor-core kernels."""

@@ -16,7 +16,7 @@ sizes `dim` (queries, keys) and `vdim` (values), and x the mixer's input:
 Nothing is rotated: positions enter through the mask and the bias alone.  q, k, v and the gates are one product.  The
 request's state is the last taps - 1 projected inputs of every channel (float, in the cache manager's state slots); the cache
 plane holds the normed keys and the values, in pages that a window gives back once it has passed them, except the pages of
-the kept first tokens.  The bias table is expanded when the weights are loaded into one row a distance (up to D, behind
+the kept first tokens.  The bias table is expanded when the weights are loaded into one entry a head and distance (up to D, behind
 which every distance falls into the last bucket), so the attention kernels look a distance up and compute no logarithm.
 """
 from __future__ import annotations
@@ -109,7 +109,8 @@ class ConvBiasAttention(Mixer):
             self._check_bias()
             last = int(math.ceil(self.bias_max))      # from here on every distance falls into the last bucket
             rows_of = [distance_bucket(n, self.bias_rows, self.bias_max) for n in range(last)] + [self.bias_rows - 1]
-            self.dist_bias = rel[torch.as_tensor(rows_of, dtype=torch.long, device=rel.device)].contiguous()
+            # [heads, distances]: a query's neighbouring keys read neighbouring floats
+            self.dist_bias = rel[torch.as_tensor(rows_of, dtype=torch.long, device=rel.device)].t().contiguous()
         if self.wo.is_cuda:
             self._pairs = kernels.decode_pairs_counter(self.wo.device)
 
