@@ -656,10 +656,10 @@ def design_run(design: str, widths, pk=None, layers: int = 16) -> dict:
                     seen = sum(min(i, le[0]["mask"]["size"] - 1) + 1 + max(0, min(le[0]["mask"]["keep_first"], i - le[0]["mask"]["size"] + 1))
                                for i in range(PROMPT_LEN)) if le else 0
                     flops = sum(2 * seen * m["heads"] * (m["dim"] + m["vdim"]) for m in le)
-                    if own.get("attention_prefill") and flops:
-                        r["prefill_2048"]["window_attention_ms"] = own["attention_prefill"]
+                    if own.get("attention_prefill_window_bias") and flops:
+                        r["prefill_2048"]["window_attention_ms"] = own["attention_prefill_window_bias"]
                         r["prefill_2048"]["window_attention_frac_of_bf16_peak"] = round(
-                            flops / (own["attention_prefill"] * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+                            flops / (own["attention_prefill_window_bias"] * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
                     lat = [l["mixer"] for l in cfg["layers"] if l["type"] == "latent_attention"]
                     ms = sum(v for k, v in own.items() if k in ("attention_prefill_tma", "attention_prefill_tc5"))
                     if lat and ms:

@@ -110,6 +110,11 @@ __device__ __forceinline__ float score2(float raw, float sc, const HeadEpilogue&
 __device__ __forceinline__ float dist_term(const HeadEpilogue& ep, int dist, int head, int nh) {
   return ep.dist_bias ? ep.dist_bias[(size_t)min(head, nh - 1) * ep.dist_rows + min(dist, ep.dist_rows - 1)] * LOG2E : 0.f;
 }
+// The same through a head's row of the table, found once (null: no bias).
+__device__ __forceinline__ const float* dist_row(const HeadEpilogue& ep, int head, int nh) {
+  return ep.dist_bias ? ep.dist_bias + (size_t)min(head, nh - 1) * ep.dist_rows : nullptr;
+}
+__device__ __forceinline__ float dist_term(const float* row, int dist, int last) { return row ? row[min(dist, last)] * LOG2E : 0.f; }
 // Kept first keys beside a window: a kernel that walks ONE range of keys walks a virtual one, the kept keys [0, kept) rounded
 // up to whole tiles and, right behind them, the window's keys; `real()` turns a virtual key into its position.  With nothing
 // kept, or where the two ranges meet, virtual and real keys are the same.

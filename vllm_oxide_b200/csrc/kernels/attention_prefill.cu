@@ -80,6 +80,7 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
   WarpSoftmax st;
   st.clear();
   const float sc = scale * LOG2E;
+  const float* brow[2] = {dist_row(ep, rhead[0], nh), dist_row(ep, rhead[1], nh)};
   // kept first keys that lie below the block's first window key come in front, as whole tiles of a virtual key range
   // (see KeptKeys); `start` and the tiles behind it are virtual keys
   const int keep = min(ep.keep_first, key_lo);
@@ -127,7 +128,7 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
             const int key = k0 + i * 8 + tq * 2 + (e & 1);
             bool ok = rvalid[h] && key <= rpos[h];
             ok = ok && (key >= first_key(rpos[h], window, ep) || key < ep.keep_first);
-            s[i][e] = ok ? score2(s[i][e], sc, ep) + dist_term(ep, rpos[h] - key, rhead[h], nh) : -INFINITY;
+            s[i][e] = ok ? score2(s[i][e], sc, ep) + dist_term(brow[h], rpos[h] - key, ep.dist_rows - 1) : -INFINITY;
           }
         }
         softmax_pv_16keys(st, s, stage + PF_TILE * ROW_BYTES + sub * 16 * ROW_BYTES, lane);
@@ -318,6 +319,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   for (int j = 0; j < DTILES; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   const float sc = scale * LOG2E;
   const int mi = lane >> 3, r8 = lane & 7;
+  const float* brow[2] = {dist_row(ep, rhead[0], nh), dist_row(ep, rhead[1], nh)};
 
   for (int it = 0; it < n_tiles; ++it) {
     const int s = it % PT_STAGES;
@@ -346,7 +348,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       }
       // mask only where the tile touches the diagonal, the window's edge, the range's ends or missing rows
       const bool need_mask = !all_rows || k0 + PT_TILE - 1 > w_pos_lo || k0 < key_lo ||
-                             k0 < first_key(w_pos_hi, window, ep) || ep.dist_bias != nullptr;
+                             k0 < first_key(w_pos_hi, window, ep);
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -356,7 +358,17 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
             const int key = k0 + i * 8 + tq * 2 + (e & 1);
             bool okk = rvalid[h] && key <= rpos[h] && (key >= key_lo || key < keep);
             okk = okk && (key >= first_key(rpos[h], window, ep) || key < ep.keep_first);
-            sv[i][e] = okk ? score2(sv[i][e], sc, ep) + dist_term(ep, rpos[h] - key, rhead[h], nh) : -INFINITY;
+            sv[i][e] = okk ? score2(sv[i][e], sc, ep) + dist_term(brow[h], rpos[h] - key, ep.dist_rows - 1) : -INFINITY;
+          }
+      } else if (ep.dist_bias) {
+        // every key of the tile is seen by every row: the bias alone is looked up, two neighbouring keys at a time
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            const int key = k0 + i * 8 + tq * 2 + (e & 1);
+            sv[i][e] = sv[i][e] * sc + dist_term(brow[h], rpos[h] - key, ep.dist_rows - 1);
           }
       } else {
 #pragma unroll

@@ -738,7 +738,8 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
         ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(pairs if map_k is not None else None),
         int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div), int(out.dtype == torch.float32),
         int(keep_first), _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[1], _p(err), _stream()),
-        "attention_decode_tma" if map_k is not None else "attention_decode")
+        "attention_decode_tma" if map_k is not None else
+        ("attention_decode_window_bias" if keep_first or dist_bias is not None else "attention_decode"))
 
 
 def decode_pairs_counter(device) -> torch.Tensor:
@@ -785,7 +786,8 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
         block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[2], window,
         ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), *extras, int(keep_first), _p(dist_bias),
         0 if dist_bias is None else dist_bias.shape[1], _p(err), _stream()),
-        "attention_prefill_tma" if map_k is not None else "attention_prefill")
+        ("attention_prefill_window_bias" if keep_first or dist_bias is not None else
+         ("attention_prefill_tma" if map_k is not None else "attention_prefill")))
 
 
 def gemm_f32(a, w, out, bias=None) -> None:
