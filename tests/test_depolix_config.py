@@ -131,23 +131,24 @@ def test_kept_first_pages_stay_while_a_window_gives_the_others_back():
 
 
 def test_distance_buckets():
-    rows, far = 32, 240.0
-    got = [distance_bucket(n, rows, far) for n in range(300)]
-    assert got[:16] == list(range(16)) and got[16] == 16 and got[239] == 31 and got[240] == 31 and got[299] == 31
-    assert all(b >= a for a, b in zip(got, got[1:])) and set(got) == set(range(32))
-    assert got == [P.distance_bucket(n, rows, far) for n in range(300)]
-    # the boundary of bucket 16 + j lies where 16 * 15^(j / 16) is reached
-    for j in range(1, 16):
-        edge = 16.0 * 15.0 ** (j / 16.0)
-        assert got[math.ceil(edge)] >= 16 + j > got[math.floor(edge) - 1]
+    rows, far = 24, 300.0
+    got = [distance_bucket(n, rows, far) for n in range(400)]
+    assert got[:12] == list(range(12)) and got[12] == 12 and got[299] == 23 and got[300] == 23 and got[399] == 23
+    assert all(b >= a for a, b in zip(got, got[1:])) and set(got) == set(range(24))
+    assert got == [P.distance_bucket(n, rows, far) for n in range(400)]
+    # the boundary of bucket 12 + j lies where 12 * 25^(j / 12) is reached
+    for j in range(1, 12):
+        edge = 12.0 * 25.0 ** (j / 12.0)
+        assert got[math.ceil(edge)] >= 12 + j > got[math.floor(edge) - 1]
 
 
 def test_stretched_frequencies_and_rotation_of_halves():
-    f, amp = scaled_frequencies(16, 500000.0, {"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0}, precise=True)
-    want, want_amp = P.stretched_frequencies(16, 500000.0, {"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0})
-    assert torch.allclose(f.double(), want, rtol=1e-7, atol=0) and amp == pytest.approx(want_amp) == pytest.approx(0.1 * math.log(2.0) + 1.0)
+    stretch = {"factor": 3.0, "original": 1024, "fast": 24.0, "slow": 2.0}
+    f, amp = scaled_frequencies(24, 250000.0, stretch, precise=True)
+    want, want_amp = P.stretched_frequencies(24, 250000.0, stretch)
+    assert torch.allclose(f.double(), want, rtol=1e-7, atol=0) and amp == pytest.approx(want_amp) == pytest.approx(0.1 * math.log(3.0) + 1.0)
     # the fastest wave is left alone, the slowest is slowed by the whole factor
-    assert float(want[0]) == 1.0 and float(want[-1]) == pytest.approx(500000.0 ** (-14.0 / 16.0) / 2.0)
+    assert float(want[0]) == 1.0 and float(want[-1]) == pytest.approx(250000.0 ** (-22.0 / 24.0) / 3.0)
     x = torch.arange(12.0, dtype=torch.float64).reshape(1, 12)
     y = P.rotate_halves(x, torch.tensor([3]), torch.tensor([0.5, 0.25], dtype=torch.float64), 2.0)
     c, s = 2.0 * math.cos(1.5), 2.0 * math.sin(1.5)

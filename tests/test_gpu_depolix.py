@@ -69,8 +69,8 @@ CONFIGS = {
     # head sizes the tensor-core kernels take; as many key heads as heads; one expert chosen; a window of one page that keeps a
     # whole page and three tokens; nothing of the shared part left unrotated; pages of 64
     "B": dict(block_size=64, config=_model(384, 128, 1e-6, [
-        _moe(_sides(_left(4, 4, 64, 64, 4, 0.125, 64, 67, 32, 240.0), _right(2, 1, 64, 64, 3, 16, 16)), 64, 1.0, 5, 1),
-        _dense(_latent(4, 64, 32, 64, 48, 96, 0.11, 500000.0, scaling={"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0}), 192, 1.5),
+        _moe(_sides(_left(4, 4, 64, 64, 4, 0.125, 64, 67, 24, 300.0), _right(2, 1, 64, 64, 3, 16, 16)), 64, 1.0, 5, 1),
+        _dense(_latent(4, 64, 32, 64, 48, 96, 0.11, 250000.0, scaling={"factor": 3.0, "original": 1024, "fast": 24.0, "slow": 2.0}), 192, 1.5),
         _moe(_latent(2, 32, 64, 48, 64, 64, 0.09, 10000.0), 48, 2.5, 4, 4)], 11.3, 1.0, 0.5)),
     # one head everywhere; a window of one position (a token sees itself and the kept first); filters of one tap (no state) and
     # of six; every expert chosen; kept first tokens beyond the window's reach from the start; sizes that are no multiples of 8

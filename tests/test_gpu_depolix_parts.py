@@ -150,7 +150,7 @@ def test_latent_attention_with_rotated_halves_and_a_gate(case, dt):
 WINDOW = {
     # (D, left sizes): plain kernel in 32 bits; in bfloat16 padded to 48 (cp.async), 64 and 128 (TMA), 32 (cp.async)
     "values wider than keys": (40, dict(heads=4, kv_heads=2, dim=24, vdim=40, conv=3, scale=0.3, bias_max=50.0, rows=10, mask=dict(size=19, keep_first=4))),
-    "64 wide, keeps more than a page": (64, dict(heads=4, kv_heads=1, dim=64, vdim=64, conv=4, scale=0.15, bias_max=240.0, rows=32, mask=dict(size=40, keep_first=21))),
+    "64 wide, keeps more than a page": (64, dict(heads=4, kv_heads=1, dim=64, vdim=64, conv=4, scale=0.15, bias_max=300.0, rows=24, mask=dict(size=44, keep_first=21))),
     "128 wide, window of one tile": (48, dict(heads=2, kv_heads=2, dim=128, vdim=128, conv=2, scale=0.1, bias_max=100.0, rows=16, mask=dict(size=64, keep_first=3))),
     "nothing kept": (32, dict(heads=2, kv_heads=1, dim=32, vdim=32, conv=3, scale=0.25, bias_max=30.0, rows=8, mask=dict(size=23, keep_first=0))),
     "kept beyond the window, one tap": (32, dict(heads=2, kv_heads=2, dim=16, vdim=32, conv=1, scale=0.3, bias_max=9.0, rows=4, mask=dict(size=5, keep_first=70))),
@@ -230,14 +230,16 @@ def test_pages_and_slots_used_again_by_the_pair(dt):
         assert_close(torch.cat(got[rid]), want, dt, f"request {rid}", 3e-5 if dt == torch.float32 else 0.04)
 
 
-DELTA = [(2, 1, 16, 8, 4, 3, 5), (4, 4, 24, 20, 2, 8, 2), (2, 2, 64, 16, 5, 16, 16), (3, 1, 128, 12, 4, 4, 6), (1, 1, 200, 36, 3, 7, 9), (2, 2, 8, 40, 1, 2, 3)]
+# (the last: ranks and a width that the weight-streaming product takes, so that a decoding step's second, small products read
+# their low-rank inputs as columns of the first product's row and write theirs behind it)
+DELTA = [(8, 4, 16, 8, 2, 64, 64), (2, 1, 16, 8, 4, 3, 5), (4, 4, 24, 20, 2, 8, 2), (2, 2, 64, 16, 5, 16, 16), (3, 1, 128, 12, 4, 4, 6), (1, 1, 200, 36, 3, 7, 9), (2, 2, 8, 40, 1, 2, 3)]
 
 
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("heads, kv, dim, vdim, taps, decay_rank, gate_rank", DELTA)
 def test_delta_rule_with_a_decay_per_key_channel(heads, kv, dim, vdim, taps, decay_rank, gate_rank, dt):
     from vllm_oxide_b200.parts import PartSpec, build_part
-    D = 40
+    D = 128 if decay_rank == 64 else 40
     part = build_part("mixer", PartSpec("gated_delta", dict(hidden_size=D, num_heads=heads, num_kv_heads=kv, dim=dim, vdim=vdim, taps=taps,
                                                             eps=1e-5, prefix="m.", decay_rank=decay_rank, gate_rank=gate_rank, gate="sigmoid")),
                       dtype=dt, device=DEV)
