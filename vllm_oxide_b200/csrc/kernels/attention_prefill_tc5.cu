@@ -109,8 +109,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   const int blk_pos_lo = first_pos + tok_base, blk_pos_hi = first_pos + min(tok_base + NQ * TT, n) - 1;
   const int key_lo = first_key(blk_pos_lo, window, ep);
   const int key_end = blk_pos_hi + 1;
-  const int start = key_lo / F5_TILE * F5_TILE;
-  const int n_tiles = (key_end - start + F5_TILE - 1) / F5_TILE;
+  // kept first keys below the block's first window key come in front, as whole tiles of a virtual key range (see KeptKeys):
+  // `start` and the steps behind it are virtual keys; with kept keys every query tile takes part from the first step on
+  // (the steps between the kept keys and its own window are masked for it: at most the tiles by which two query tiles'
+  // windows differ)
+  const int keep = min(ep.keep_first, key_lo);
+  int start = key_lo / F5_TILE * F5_TILE;
+  const KeptKeys km = kept_keys(keep, F5_TILE, start);
+  const int n_tiles = (key_end - km.gap - start + F5_TILE - 1) / F5_TILE;
   // the steps that each query tile takes part in: [jlo, jhi)
   int jlo[NQ], jhi[NQ];
 #pragma unroll
@@ -119,14 +125,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     if (tok_first >= n) { jlo[qt] = jhi[qt] = 0; continue; }
     const int pos_lo = first_pos + tok_first, pos_hi = first_pos + min(tok_first + TT, n) - 1;
     const int klo = first_key(pos_lo, window, ep);
-    jlo[qt] = (klo - start) / F5_TILE;
-    jhi[qt] = (pos_hi - start) / F5_TILE + 1;
+    jlo[qt] = ep.keep_first > 0 ? 0 : (klo - start) / F5_TILE;      // (kept keys may also lie inside the block's own range)
+    jhi[qt] = (pos_hi - km.gap - start) / F5_TILE + 1;
   }
 
   // the producer asks for the pages of its first tiles now (the block tables were written before the step began), so
   // that the look-up runs beside the set-up below
   WarpPages wp;
-  if (warp == 4 * NQ) wp.advance(table, block_size, start, 0, lane, key_lo, key_end);
+  if (warp == 4 * NQ) wp.advance(table, block_size, start, 0, lane, key_lo, key_end, km, keep);
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], NQ); }
     for (int i = 0; i < 2 * NQ; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); }
@@ -200,14 +206,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     int it = 0;
     for (; it < n_tiles; ++it) {
       const int s = it % ST;
-      if (it > 0) wp.advance(table, block_size, start, it, lane, key_lo, key_end);
+      if (it > 0) wp.advance(table, block_size, start, it, lane, key_lo, key_end, km, keep);
       int pg[4];
 #pragma unroll
       for (int run = 0; run < 4; ++run) pg[run] = wp.page(it, run);
       if (lane == 0) {
         if (it >= ST) ok = mbar_wait(&kv_empty[s], (unsigned)(((it / ST) - 1) & 1), abort_flag, err);
         if (ok) {
-          const int tile_start = start + it * F5_TILE;
+          const int tile_start = km.real(start + it * F5_TILE);
           mbar_expect_tx(&kv_full[s], (unsigned)F5_STAGE_BYTES);
           char* kt = kv_s + s * F5_STAGE_BYTES;
           if (box_keys == F5_TILE) {
@@ -331,6 +337,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + qt * C::TILE_COLS;
     const float sc = scale * LOG2E;
     const int row_lo = first_key(rpos, window, ep);
+    // a bias by distance, divided by the scale as well: one look-up a score in the head's row of the table
+    const float* brow = dist_row(ep, head, nh);
+    const float bias_raw = LOG2E / sc;
+    const int last_dist = ep.dist_rows - 1;
     // a capped score, divided by the scale again: the steps below take maxima of raw products and scale them afterwards
     const float cap_raw = ep.cap_out > 0.f ? ep.cap_out / sc : 0.f, cap_raw2 = -2.f * cap_raw;
     float m_ref = -INFINITY, l = 0.f;
@@ -342,9 +352,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       t5_fence_after();
-      const int k0 = start + j * F5_TILE;
-      // mask only where the step touches the diagonal, the window's edge or missing rows
-      const bool need_mask = !all_rows || k0 + F5_TILE - 1 > t_pos_lo || k0 < first_key(t_pos_hi, window, ep);
+      const int k0 = km.real(start + j * F5_TILE);
+      // mask only where the step touches the diagonal, the window's edge or missing rows (a step of kept keys alone has
+      // no window's edge)
+      const bool need_mask = !all_rows || k0 + F5_TILE - 1 > t_pos_lo ||
+                             (k0 < first_key(t_pos_hi, window, ep) && k0 + F5_TILE > ep.keep_first);
       // (the rows past TR of a whole tile hold zeros: their scores are finite and go nowhere)
       float s[64];
       // the row's 64 scores of this step from tensor memory, masked
@@ -363,8 +375,13 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
 #pragma unroll
           for (int c = 0; c < 64; ++c) {
             const int key = k0 + c;
-            s[c] = (valid && key <= rpos && key >= row_lo) ? s[c] : -INFINITY;
+            const bool seen = valid && key <= rpos && (key >= row_lo || key < ep.keep_first);
+            s[c] = seen ? (brow ? fmaf(brow[min(rpos - key, last_dist)], bias_raw, s[c]) : s[c]) : -INFINITY;
           }
+        } else if (brow) {
+          // every key of the step lies at or before every row's position
+#pragma unroll
+          for (int c = 0; c < 64; ++c) s[c] = fmaf(brow[min(rpos - (k0 + c), last_dist)], bias_raw, s[c]);
         }
       };
       // the maximum of the raw scores (the scale is positive): four chains of three-input maxima
@@ -547,14 +564,18 @@ VOB_API int vob_attention_prefill_has_tc5() {
 // As vob_attention_prefill_tma (same tensor maps: 64-column slices, boxes of vob_attention_decode_box_keys rows), for
 // head sizes 64 and 128.  `query_tiles` is 1 or 2: how many tiles of 128 query rows a block takes.  `sink`: the softmax has a
 // silent extra entry of score 0; `gate` (bfloat16, may be null): head h of token t is multiplied by
-// sigmoid(gate[t * gate_stride + h]).  `softcap`, `chunk`, `value_div`, `out_float`: as for vob_attention_prefill_ex.
+// sigmoid(gate[t * gate_stride + h]).  `softcap`, `chunk`, `value_div`, `out_float`, `keep_first`, `dist_bias`: as for
+// vob_attention_prefill_ex.
 VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, const void* map_q, const void* map_o, const void* q, long q_stride, void* out,
                                       const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
                                       int num_requests, int max_q, int nh, int kvh, int block_size, int window, float scale,
                                       long num_pages, int query_tiles, int sink, const void* gate, long gate_stride,
-                                      float softcap, int chunk, int value_div, int out_float, int* err, cudaStream_t stream) {
+                                      float softcap, int chunk, int value_div, int out_float, int keep_first,
+                                      const float* dist_bias, int dist_rows, int* err, cudaStream_t stream) {
 #if VOB_HD == 64 || VOB_HD == 128
-  const HeadEpilogue ep = head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float);
+  const HeadEpilogue ep = head_options(sink, gate, gate_stride, softcap, scale, chunk, value_div, out_float, keep_first, dist_bias,
+                                       dist_rows);
+  if (keep_first < 0 || (dist_bias && dist_rows <= 0)) return VOB_BAD_ARGUMENT;
   if (out_float && map_o) return VOB_BAD_ARGUMENT;           // whole tiles leave by the copy engine as bfloat16 only
   if (value_div > 1 && kvh % value_div) return VOB_BAD_ARGUMENT;
   if (num_requests <= 0 || max_q <= 1) return 0;

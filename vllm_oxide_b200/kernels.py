@@ -756,11 +756,9 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
     tensor cores (`use_tc5`; `tiles_by_tma` False makes that kernel bring its query tiles in by cp.async and store its
     output row by row also where TMA could), other multiples of 64 on mma.sync with TMA copies (`use_tma`), the rest with
     cp.async.  `sink`, `gate`, `gate_stride`, `softcap`, `chunk`: as for paged_attention_generic; `value_div`: as for
-    attention_decode.  `keep_first`, `dist_bias`: as for paged_attention_generic; with either the mma.sync kernel with
-    cp.async copies runs, whatever the head size."""
+    attention_decode.  `keep_first`, `dist_bias`: as for paged_attention_generic; all three kernels take them."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, gate, dist_bias)
     assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape[0] == nh)
-    use_tc5 = use_tc5 and not keep_first and dist_bias is None
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
     L = attention_lib(hd)
     extras = (int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), ctypes.c_float(softcap), int(chunk), int(value_div),
@@ -779,7 +777,9 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
             _check(L.vob_attention_prefill_tc5(
                 map_k, map_v, map_q, map_o, _p(q), ctypes.c_long(q_stride), _p(out), _p(block_tables), block_tables.shape[-1], _p(cu_q),
                 _p(context_lens), num_requests, max_q, nh, kvh, bs, window, ctypes.c_float(scale),
-                ctypes.c_long(kcache.shape[0]), query_tiles, *extras, _p(err), _stream()), "attention_prefill_tc5")
+                ctypes.c_long(kcache.shape[0]), query_tiles, *extras, int(keep_first), _p(dist_bias),
+                0 if dist_bias is None else dist_bias.shape[1], _p(err), _stream()),
+                "attention_prefill_window_bias" if keep_first or dist_bias is not None else "attention_prefill_tc5")
             return
     _check(L.vob_attention_prefill_ex(
         map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
