@@ -39,13 +39,22 @@ __global__ void clamped_glu_vec_kernel(const T* gu, long gu_stride, const float*
   float g[N], u[N], y[N];
   Wide16<T>::load(gu + t * gu_stride + i, g);
   Wide16<T>::load(gu + t * gu_stride + I + i, u);
+  if (bias) {
+    // (I and i are multiples of four: the biases come four at a time)
+#pragma unroll
+    for (int j = 0; j < N; j += 4) {
+      const float4 bg = *reinterpret_cast<const float4*>(bias + i + j), bu = *reinterpret_cast<const float4*>(bias + I + i + j);
+      g[j] += bg.x; g[j + 1] += bg.y; g[j + 2] += bg.z; g[j + 3] += bg.w;
+      u[j] += bu.x; u[j + 1] += bu.y; u[j + 2] += bu.z; u[j + 3] += bu.w;
+    }
+  }
 #pragma unroll
   for (int j = 0; j < N; ++j) {
-    float a = g[j], b = u[j];
-    if (bias) { a += bias[i + j]; b += bias[I + i + j]; }
-    a = fminf(a, limit);
-    b = fminf(fmaxf(b, -limit), limit);
-    y[j] = a / (1.f + expf(-alpha * a)) * (b + 1.f);
+    const float a = fminf(g[j], limit), b = fminf(fmaxf(u[j], -limit), limit);
+    // bfloat16 rows: the hardware's exponential and division, as SiLU * up takes them for portions (a float unit or two
+    // before a rounding to 8 bits); float rows: the accurate ones
+    if (sizeof(T) == 2) y[j] = __fdividef(a, 1.f + __expf(-alpha * a)) * (b + 1.f);
+    else y[j] = a / (1.f + expf(-alpha * a)) * (b + 1.f);
   }
   Wide16<T>::store(out + t * I + i, y);
 }
@@ -70,7 +79,7 @@ VOB_API int vob_clamped_glu(const void* gu, long gu_stride, const float* bias, v
   if (!(limit > 0.f)) return VOB_BAD_ARGUMENT;
   const size_t total = (size_t)T * I;
   const int n = dtype == VOB_F32 ? 4 : 8;
-  if (I % n == 0 && gu_stride % n == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+  if (I % n == 0 && gu_stride % n == 0 && (((uintptr_t)gu | (uintptr_t)out | (uintptr_t)bias) & 15) == 0) {
     const size_t chunks = total / n;
     const dim3 vgrid((unsigned)((chunks + 255) / 256));
     if (dtype == VOB_F32)

@@ -190,7 +190,11 @@ __global__ void sigmoid_gate_mul_vec_kernel(T* x, long x_stride, const T* gate, 
   Wide16<T>::load(x + t * x_stride + i, v);
   Wide16<T>::load(gate + t * gate_stride + i, g);
 #pragma unroll
-  for (int j = 0; j < N; ++j) v[j] = v[j] / (1.f + expf(-g[j]));
+  for (int j = 0; j < N; ++j) {
+    // bfloat16 rows: the hardware's exponential and division (a float unit or two before a rounding to 8 bits)
+    if (sizeof(T) == 2) v[j] = __fdividef(v[j], 1.f + __expf(-g[j]));
+    else v[j] = v[j] / (1.f + expf(-g[j]));
+  }
   Wide16<T>::store(x + t * x_stride + i, v);
 }
 
