@@ -75,6 +75,9 @@ class ConvBiasAttention(Mixer):
     def _check_bias(self) -> None:
         if self.bias_rows > 0 and not (self.bias_rows >= 2 and self.bias_max > self.bias_rows // 2):
             raise ValueError(f"a distance bias of {self.bias_rows} rows needs bias_max above {self.bias_rows // 2}, not {self.bias_max}")
+        if self.bias_rows and self.bias_max > MAX_BIAS_DISTANCES:
+            raise ValueError(f"the distance table is expanded to one entry a head and distance up to bias_max: {self.bias_max} is "
+                             f"beyond the {MAX_BIAS_DISTANCES} that are built")
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, H, q, k, v = self.prefix, self.H, self.nh * self.kd, self.kvh * self.kd, self.kvh * self.vd
@@ -143,6 +146,9 @@ class ConvBiasAttention(Mixer):
                      keep_first=self.keep_first if self.window else 0, dist_bias=self.dist_bias)
         return linear(heads, self.wo, ctx.ws.get("conv_attn_proj", T, self.H, x.dtype), ctx)
 
+
+# The most distances the expanded bias table holds a head (4 MiB of floats a head).
+MAX_BIAS_DISTANCES = 1 << 20
 
 # Whether bfloat16 layers pad their heads to one size that the tensor-core kernels take (else the plain kernel runs them).
 PAD_HEADS = True
